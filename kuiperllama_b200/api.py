@@ -1,0 +1,85 @@
+"""The Python entry point: ``load`` a model folder, ``generate`` from token ids.
+
+ExiledOfCode/KuiperLLama has no Python binding; its two entry points are the C++ demo
+(``llama_infer <checkpoint> <tokenizer>``, demo/main.cpp:50-75) and the ``generate`` method of
+its PyTorch model (tools/model.py:315-343: ``generate(idx, max_new_tokens, temperature,
+top_k)``).  The names and meanings of ``max_new_tokens``, ``temperature`` (0 picks the most
+likely token) and ``top_k`` follow the latter; token ids go in and come out, as there.
+"""
+from __future__ import annotations
+
+from typing import Iterable, List, Optional, Sequence
+
+import torch
+
+from .cache import PAGE, pages_for
+from .engine.generate import EngineBackend, GenerationStats, RequestResult, run_requests
+from .engine.loading import load_model, random_model
+from .engine.model import DecoderModel
+from .engine.step import Engine
+from .sampling import Sampler, SamplingParams
+
+
+class LlamaInfer:
+    """A loaded model with its cache, step function and generation loop.
+
+    ``max_tokens`` sizes the cache: the most tokens that live sequences hold at any time,
+    each rounded up to whole pages of 64.  ``max_batch`` bounds the sequences that run
+    together; ``max_seq_len`` bounds one sequence (default: max_position_embeddings)."""
+
+    def __init__(self, model: DecoderModel, max_tokens: Optional[int] = None, max_batch: int = 64,
+                 max_seq_len: Optional[int] = None, use_graphs: bool = True):
+        self.model = model
+        self.max_seq_len = min(max_seq_len or model.spec.max_positions, model.spec.max_positions)
+        self.max_batch = max_batch
+        if max_tokens is None:
+            max_tokens = max_batch * pages_for(self.max_seq_len, PAGE) * PAGE
+        self.cache = model.new_cache(max_tokens=max_tokens, max_seq_len=self.max_seq_len)
+        self.max_seq_len = self.cache.max_seq_len
+        self.engine = Engine(model, self.cache, use_graphs=use_graphs)
+        self.last_stats: Optional[GenerationStats] = None
+        self.last_results: Optional[List[RequestResult]] = None
+
+    @property
+    def stop_token_ids(self):
+        return self.model.spec.stop_token_ids
+
+    @torch.inference_mode()
+    def generate(self, prompts: Sequence[Sequence[int]], max_new_tokens: int, temperature: float = 0.0,
+                 top_k: Optional[int] = None, seed: int = 0, stop_ids: Optional[Iterable[int]] = None,
+                 include_stop: bool = False) -> List[List[int]]:
+        """New token ids for every prompt (lists of token ids), in the order given.
+
+        ``temperature`` 0 is greedy; otherwise softmax(logits / temperature) after an optional
+        ``top_k`` cut, drawn with a generator keyed by (seed, index of the prompt, step).
+        ``stop_ids`` default to the configuration's eos ids; a stop token ends its sequence
+        and is left out unless ``include_stop``."""
+        single = len(prompts) > 0 and isinstance(prompts[0], int)
+        if single:
+            prompts = [prompts]
+        sampler = Sampler(SamplingParams(temperature=float(temperature), top_k=top_k, seed=int(seed)))
+        stats = GenerationStats()
+        results = run_requests(EngineBackend(self.engine, sampler), [list(p) for p in prompts], int(max_new_tokens),
+                               stop_ids=self.stop_token_ids if stop_ids is None else stop_ids,
+                               include_stop=include_stop, max_batch=self.max_batch,
+                               token_budget=self.cache.n_pages * PAGE, max_seq_len=self.max_seq_len, stats=stats)
+        self.last_stats, self.last_results = stats, results
+        out = [r.tokens for r in results]
+        return out[0] if single else out
+
+
+def load(path: Optional[str] = None, dtype: str = "bfloat16", device: str = "cuda:0", *, config=None,
+         random_weights: bool = False, seed: int = 0, max_tokens: Optional[int] = None, max_batch: int = 64,
+         max_seq_len: Optional[int] = None, use_graphs: bool = True) -> LlamaInfer:
+    """Load the model folder ``path`` (config.json + model.safetensors).  With
+    ``random_weights`` and a ``config`` object, build a random model on the device instead."""
+    if random_weights:
+        if config is None:
+            from .config import config_from_folder
+            config = config_from_folder(path)
+        model = random_model(config, seed, dtype=dtype, device=device)
+    else:
+        if path is None:
+            raise ValueError("load() needs a model folder, or random_weights=True with a config")
+        model = load_model(path, dtype=dtype, device=device)
+    return LlamaInfer(model, max_tokens=max_tokens, max_batch=max_batch, max_seq_len=max_seq_len, use_graphs=use_graphs)

@@ -1,0 +1,186 @@
+"""The cache of a model: a slot for each live sequence, paged keys and values for every
+execution of a layer that asks for them, and fixed-size state per slot.
+
+* A *slot* belongs to one sequence from its first token until the sequence ends; then it is
+  handed back and the next sequence reuses it, with the old contents still in the pages.
+* Keys and values live in pages of ``PAGE`` tokens.  Executions of layers whose requests
+  are equal (kind, kv heads, head size, window) form a *group*; each group has storage, a
+  page pool and a block table of its own, so layers with different needs do not share a
+  layout.  The storage of one execution is ``[pages, kv_heads, PAGE, head_dim]``.
+* Beside the pages every execution may ask for per-slot state of a fixed shape (a
+  recurrent mixer's state, for instance).  It is zeroed when a slot is handed out.  The
+  dense Llama decoder asks for none.
+
+ExiledOfCode/KuiperLLama keeps two float32 tensors [layers, seq_len, kv_dim] for its single
+sequence (kuiper/source/model/llama3.cpp:468-474, model.cpp:221-238).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from .allocators import CacheError, FreeList, pages_for
+
+PAGE = 64      # tokens per page; the kernels are compiled for the same number
+
+
+@dataclass(frozen=True)
+class KVRequest:
+    """Token-indexed storage a mixer asks for.  ``kind`` "full": every key is kept.
+    ``window`` is the number of most recent keys the mixer reads (None: all)."""
+    kv_heads: int
+    head_dim: int
+    kind: str = "full"
+    window: Optional[int] = None
+
+
+@dataclass(frozen=True)
+class StateRequest:
+    """Per-slot state of a fixed shape that a mixer asks for."""
+    shape: Tuple[int, ...]
+    dtype: torch.dtype = torch.float32
+
+
+@dataclass
+class CacheView:
+    """What one execution of a layer sees of the cache."""
+    k: Optional[torch.Tensor]             # [pages, kv_heads, PAGE, head_dim] or None
+    v: Optional[torch.Tensor]
+    block_table: Optional[torch.Tensor]   # int32 [slots, blocks_per_seq] of the group
+    state: Optional[torch.Tensor]         # [slots, *shape] or None
+    writable: bool                        # False: the execution reads another one's cache
+
+
+class _Group:
+    def __init__(self, request: KVRequest, entries: List[int], n_pages: int, n_slots: int, blocks_per_seq: int,
+                 dtype: torch.dtype, device: torch.device):
+        if request.kind != "full":
+            raise CacheError(f"cache kind {request.kind!r} is not known (known: 'full')")
+        self.request = request
+        self.entries = entries
+        self.pages = FreeList(n_pages, "page")
+        self.blocks_per_seq = blocks_per_seq
+        shape = (len(entries), n_pages, request.kv_heads, PAGE, request.head_dim)
+        self.k = torch.zeros(shape, dtype=dtype, device=device)
+        self.v = torch.zeros(shape, dtype=dtype, device=device)
+        # Pageable on purpose: a copy from pageable memory is staged before the call returns,
+        # so the host may rewrite a row (a slot that is reused) while an earlier step's copy
+        # is still queued on the device.
+        self.table_host = torch.zeros((n_slots, blocks_per_seq), dtype=torch.int32)
+        self.table = torch.zeros((n_slots, blocks_per_seq), dtype=torch.int32, device=device)
+        self.slot_pages: List[List[int]] = [[] for _ in range(n_slots)]
+        self.dirty: set = set()
+
+
+class SequenceCache:
+    """``max_tokens`` is the most tokens that live sequences hold at any time, each
+    sequence's count rounded up to a multiple of ``PAGE``; it sizes every group's pool.
+    ``max_seq_len`` bounds one sequence.  ``kv_requests[i]`` / ``state_requests[i]`` are the
+    requests of schedule entry i (None: nothing); ``cache_from[i]`` names an earlier entry
+    whose storage entry i reads instead of owning some."""
+
+    def __init__(self, kv_requests: Sequence[Optional[KVRequest]],
+                 state_requests: Sequence[Optional[StateRequest]], cache_from: Sequence[Optional[int]],
+                 max_tokens: int, max_seq_len: int, dtype: torch.dtype, device, max_slots: Optional[int] = None):
+        if max_tokens < PAGE:
+            raise CacheError(f"max_tokens {max_tokens} is less than one page of {PAGE} tokens")
+        self.device = torch.device(device)
+        self.dtype = dtype
+        self.n_pages = max_tokens // PAGE
+        self.max_seq_len = min(max_seq_len, self.n_pages * PAGE)
+        self.n_slots = self.n_pages if max_slots is None else max(1, min(max_slots, self.n_pages))
+        self.blocks_per_seq = pages_for(self.max_seq_len, PAGE)
+        self.slots = FreeList(self.n_slots, "slot")
+        self.lengths: List[int] = [0] * self.n_slots
+        self.cache_from = list(cache_from)
+
+        # group the executions that own storage by their request
+        by_request: Dict[KVRequest, List[int]] = {}
+        for i, (req, src) in enumerate(zip(kv_requests, cache_from)):
+            if req is not None and src is None:
+                by_request.setdefault(req, []).append(i)
+        self.groups: List[_Group] = [
+            _Group(req, entries, self.n_pages, self.n_slots, self.blocks_per_seq, dtype, self.device)
+            for req, entries in by_request.items()]
+        self._where: Dict[int, Tuple[_Group, int]] = {}
+        for g in self.groups:
+            for j, e in enumerate(g.entries):
+                self._where[e] = (g, j)
+        for i, (req, src) in enumerate(zip(kv_requests, cache_from)):
+            if src is not None and req is not None:
+                if src not in self._where:
+                    raise CacheError(f"schedule entry {i} reads the cache of entry {src}, which owns none")
+                if self._where[src][0].request != req:
+                    raise CacheError(f"schedule entry {i} reads the cache of entry {src}, whose layout differs")
+
+        self.states: Dict[int, torch.Tensor] = {}
+        for i, (sreq, src) in enumerate(zip(state_requests, cache_from)):
+            if sreq is not None and src is None:
+                self.states[i] = torch.zeros((self.n_slots,) + tuple(sreq.shape), dtype=sreq.dtype, device=self.device)
+
+    # ------------------------------------------------------------------ slots
+    def alloc_slot(self) -> int:
+        slot = self.slots.take()
+        self.lengths[slot] = 0
+        for st in self.states.values():
+            st[slot].zero_()
+        return slot
+
+    def free_slot(self, slot: int) -> None:
+        if not self.slots.is_held(slot):
+            raise CacheError(f"slot {slot} is freed but is not held")
+        for g in self.groups:
+            for p in reversed(g.slot_pages[slot]):
+                g.pages.give_back(p)
+            g.slot_pages[slot] = []
+        self.lengths[slot] = 0
+        self.slots.give_back(slot)
+
+    def reserve(self, slot: int, new_length: int) -> None:
+        """Make room for the sequence in ``slot`` to hold ``new_length`` tokens."""
+        if not self.slots.is_held(slot):
+            raise CacheError(f"slot {slot} is not held")
+        if new_length > self.max_seq_len:
+            raise CacheError(f"a sequence of {new_length} tokens exceeds the cache's limit of {self.max_seq_len}")
+        need = pages_for(new_length, PAGE)
+        for g in self.groups:
+            have = g.slot_pages[slot]
+            if need > len(have):
+                fresh = g.pages.take_many(need - len(have))
+                for p in fresh:
+                    g.table_host[slot, len(have)] = p
+                    have.append(p)
+                g.dirty.add(slot)
+
+    def flush_tables(self) -> None:
+        """Bring the device's block tables up to date (copies on the current stream)."""
+        for g in self.groups:
+            if not g.dirty:
+                continue
+            lo, hi = min(g.dirty), max(g.dirty) + 1
+            g.table[lo:hi].copy_(g.table_host[lo:hi], non_blocking=True)
+            g.dirty.clear()
+
+    # ------------------------------------------------------------------ views
+    def view(self, entry: int) -> CacheView:
+        src = self.cache_from[entry]
+        owner = entry if src is None else src
+        k = v = table = None
+        if owner in self._where:
+            g, j = self._where[owner]
+            k, v, table = g.k[j], g.v[j], g.table
+        return CacheView(k=k, v=v, block_table=table, state=self.states.get(owner), writable=src is None)
+
+    # ------------------------------------------------------------------ accounting
+    def held_tokens(self) -> int:
+        """Tokens held by live sequences, each rounded up to whole pages."""
+        return sum(pages_for(self.lengths[s], PAGE) * PAGE for s in range(self.n_slots) if self.slots.is_held(s))
+
+    def pages_held(self) -> List[int]:
+        return [g.pages.held() for g in self.groups]
+
+    def bytes(self) -> int:
+        n = sum(g.k.numel() * g.k.element_size() * 2 for g in self.groups)
+        return n + sum(s.numel() * s.element_size() for s in self.states.values())

@@ -1,0 +1,102 @@
+// Shared helpers of the kuiperllama_b200 kernels (sm_100a).
+//
+// Every kernel file exports plain C entry points that take raw device pointers, sizes and
+// a cudaStream_t, allocate nothing and return 0 or an error code; the Python side
+// (csrc/ops.py) checks shapes and types before it calls them.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define KL_API extern "C" __attribute__((visibility("default")))
+
+// Return codes of the C entry points.
+enum : int {
+    KL_OK = 0,
+    KL_ERR_BAD_DTYPE = -1,      // a dtype code the kernel has no instance for
+    KL_ERR_BAD_SIZE = -2,       // a size the kernel refuses (message printed to stderr)
+    KL_ERR_BAD_ALIGN = -3,      // a pointer or stride that is not aligned as the kernel needs
+    KL_ERR_DEVICE_STATUS = -4,  // a kernel reported through its status word (bounded wait ran out)
+    KL_ERR_SETUP = -5,          // a driver or runtime call at set-up failed
+};
+
+// dtype codes shared with csrc/ops.py
+enum : int { KL_F32 = 0, KL_BF16 = 1 };
+
+#define KL_LAUNCH_CHECK()                                  \
+    do {                                                   \
+        cudaError_t e__ = cudaGetLastError();              \
+        if (e__ != cudaSuccess) return (int)e__;           \
+    } while (0)
+
+#define KL_CUDA(call)                                      \
+    do {                                                   \
+        cudaError_t e__ = (call);                          \
+        if (e__ != cudaSuccess) return (int)e__;           \
+    } while (0)
+
+namespace kl {
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ float to_f32(float v) { return v; }
+__device__ __forceinline__ float to_f32(bf16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 from_f32<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a CTA whose size is a multiple of 32 (at most 1024 threads).  Every thread gets
+// the result.  `scratch` holds 33 floats of shared memory.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();                       // scratch may still be read from an earlier call
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < nwarps ? scratch[lane] : 0.f;
+        t = warp_sum(t);
+        if (lane == 0) scratch[32] = t;
+    }
+    __syncthreads();
+    return scratch[32];
+}
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < nwarps ? scratch[lane] : -INFINITY;
+        t = warp_max(t);
+        if (lane == 0) scratch[32] = t;
+    }
+    __syncthreads();
+    return scratch[32];
+}
+
+// Paged cache addressing.  One cache entry (one execution of a layer) stores keys (or
+// values) as [n_pages][kv_heads][PAGE][head_dim]; a sequence's logical block b lives in page
+// block_table[slot * blocks_per_seq + b].
+constexpr int PAGE = 64;
+
+__device__ __forceinline__ size_t cache_row_offset(const int* __restrict__ block_table, int blocks_per_seq,
+                                                   int slot, int pos, int kv_head, int kv_heads, int head_dim) {
+    const int page = block_table[(size_t)slot * blocks_per_seq + (pos / PAGE)];
+    return (((size_t)page * kv_heads + kv_head) * PAGE + (pos % PAGE)) * (size_t)head_dim;
+}
+
+}  // namespace kl

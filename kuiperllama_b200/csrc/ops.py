@@ -1,0 +1,236 @@
+"""Python side of the CUDA kernels: loads each module's shared library (building it at first
+use), checks shapes, types and devices, and calls the C entry points on torch's current
+stream.  Nothing here computes on the CPU and nothing falls back to a library kernel: a
+missing extension or a refused size raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import threading
+from typing import Dict, Optional
+
+import torch
+
+from . import build
+from .build import ExtensionError
+
+PAGE = 64                      # tokens per cache page; equals kl::PAGE in common.cuh
+
+F32, BF16 = 0, 1
+_DTYPE_CODE = {torch.float32: F32, torch.bfloat16: BF16}
+
+_ERRORS = {-1: "unsupported dtype", -2: "unsupported size", -3: "misaligned pointer or stride",
+           -4: "the kernel reported an error through its status word", -5: "set-up failed"}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_libs: Dict[str, ctypes.CDLL] = {}
+_lock = threading.Lock()
+
+
+def lib(name: str) -> ctypes.CDLL:
+    """The loaded shared library of one kernel module."""
+    got = _libs.get(name)
+    if got is not None:
+        return got
+    with _lock:
+        if name not in _libs:
+            path = build.ensure_built(name)
+            try:
+                _libs[name] = ctypes.CDLL(path)
+            except OSError as e:
+                raise ExtensionError(f"cannot load {path}: {e}") from None
+        return _libs[name]
+
+
+def loaded_libraries() -> Dict[str, str]:
+    return {n: l._name for n, l in _libs.items()}
+
+
+def _check(code: int, what: str) -> None:
+    if code == 0:
+        return
+    if code in _ERRORS:
+        raise KernelError(f"{what}: {_ERRORS[code]}")
+    raise KernelError(f"{what}: CUDA error {code}")
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    try:
+        return _DTYPE_CODE[dtype]
+    except KeyError:
+        raise KernelError(f"dtype {dtype} is not supported by the kernels (float32, bfloat16)") from None
+
+
+def _ptr(t: Optional[torch.Tensor]) -> ctypes.c_void_p:
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _need(cond: bool, msg: str) -> None:
+    if not cond:
+        raise KernelError(msg)
+
+
+def _cuda(*tensors: Optional[torch.Tensor]) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError("kernel arguments must live on a CUDA device; there is no CPU path")
+
+
+def _i32(t: Optional[torch.Tensor], name: str) -> None:
+    if t is not None:
+        _need(t.dtype == torch.int32 and t.is_contiguous(), f"{name} must be a contiguous int32 tensor")
+
+
+# --------------------------------------------------------------------------- row-wise
+
+def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, error_flag: torch.Tensor) -> None:
+    """out[t] = float32(table[ids[t]]); ids outside the table set error_flag[0] = 1."""
+    _cuda(ids, table, out, error_flag)
+    _i32(ids, "ids"); _i32(error_flag, "error_flag")
+    n, (vocab, hidden) = ids.numel(), table.shape
+    _need(table.is_contiguous() and out.is_contiguous() and out.dtype == torch.float32, "embedding: bad layout")
+    _need(out.shape[0] >= n and out.shape[1] == hidden, "embedding: output shape")
+    _check(lib("rowwise").kl_embedding(_ptr(ids), n, _ptr(table), dtype_code(table.dtype), vocab, hidden,
+                                       _ptr(out), _ptr(error_flag), _stream()), "embedding")
+
+
+def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, out: torch.Tensor,
+                eps: float, rows: Optional[torch.Tensor] = None) -> None:
+    """x = residual (+ delta); out = weight * x * rsqrt(mean(x^2) + eps).
+
+    Without ``rows`` every row is processed and, when ``delta`` is given, the sum is written
+    back to ``residual``.  With ``rows`` (int32 indices) only those rows are read, into
+    out[0..len(rows)), and ``residual`` is left as it is."""
+    _cuda(residual, delta, weight, out, rows)
+    _i32(rows, "rows")
+    hidden = residual.shape[-1]
+    n = rows.numel() if rows is not None else residual.shape[0]
+    _need(residual.dtype == torch.float32 and residual.is_contiguous(), "add_rmsnorm: the residual stream is float32")
+    _need(weight.dtype == torch.float32 and weight.numel() == hidden, "add_rmsnorm: weight must be float32 [hidden]")
+    _need(out.is_contiguous() and out.shape[-1] == hidden and out.shape[0] >= n, "add_rmsnorm: output shape")
+    if delta is not None:
+        _need(delta.dtype == out.dtype and delta.is_contiguous() and delta.shape == residual.shape,
+              "add_rmsnorm: delta must match the residual's shape and the output's dtype")
+    _check(lib("rowwise").kl_add_rmsnorm(_ptr(residual), _ptr(delta), _ptr(weight), _ptr(out), _ptr(rows), n, hidden,
+                                         ctypes.c_float(eps), dtype_code(out.dtype), _stream()), "add_rmsnorm")
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]."""
+    _cuda(gate_up, out)
+    tokens, two_i = gate_up.shape
+    _need(two_i % 2 == 0 and out.shape == (tokens, two_i // 2), "swiglu: shapes")
+    _need(gate_up.is_contiguous() and out.is_contiguous() and gate_up.dtype == out.dtype, "swiglu: layout")
+    _check(lib("rowwise").kl_swiglu(_ptr(gate_up), _ptr(out), tokens, two_i // 2, dtype_code(out.dtype), _stream()),
+           "swiglu")
+
+
+# --------------------------------------------------------------------------- position encoding + cache write
+
+def rope_kv_write(qkv: torch.Tensor, inv_freq: Optional[torch.Tensor], rotary_dim: int, positions: torch.Tensor,
+                  token_slot: torch.Tensor, block_table: torch.Tensor, k_cache: Optional[torch.Tensor],
+                  v_cache: Optional[torch.Tensor], num_heads: int, num_kv_heads: int, head_dim: int) -> None:
+    """Rotate the query heads of ``qkv`` [tokens, (H + 2 KV) * hd] in place; rotate the key
+    heads and store them, and the value heads, into the paged cache
+    [pages, KV, PAGE, hd] (skipped when both caches are None)."""
+    _cuda(qkv, inv_freq, positions, token_slot, block_table, k_cache, v_cache)
+    _i32(positions, "positions"); _i32(token_slot, "token_slot"); _i32(block_table, "block_table")
+    n = qkv.shape[0]
+    _need(qkv.is_contiguous() and qkv.shape[1] == (num_heads + 2 * num_kv_heads) * head_dim, "rope_kv_write: qkv shape")
+    _need(positions.numel() >= n and token_slot.numel() >= n, "rope_kv_write: one position and slot per token")
+    write = k_cache is not None
+    if write:
+        _need(v_cache is not None and k_cache.dtype == qkv.dtype and v_cache.dtype == qkv.dtype, "rope_kv_write: cache dtype")
+        _need(k_cache.is_contiguous() and v_cache.is_contiguous()
+              and tuple(k_cache.shape[1:]) == (num_kv_heads, PAGE, head_dim) and k_cache.shape == v_cache.shape,
+              "rope_kv_write: cache layout must be [pages, kv_heads, 64, head_dim]")
+    if rotary_dim:
+        _need(inv_freq is not None and inv_freq.dtype == torch.float32 and inv_freq.numel() == rotary_dim // 2,
+              "rope_kv_write: inv_freq must be float32 [rotary_dim / 2]")
+    _check(lib("rope_kv").kl_rope_kv_write(_ptr(qkv), _ptr(inv_freq), rotary_dim, _ptr(positions), _ptr(token_slot),
+                                           _ptr(block_table), block_table.shape[1], _ptr(k_cache), _ptr(v_cache), n,
+                                           num_heads, num_kv_heads, head_dim, int(write), dtype_code(qkv.dtype),
+                                           _stream()), "rope_kv_write")
+
+
+# --------------------------------------------------------------------------- attention
+
+def attention_simt(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                   block_table: torch.Tensor, positions: torch.Tensor, token_slot: torch.Tensor, n_tokens: int,
+                   num_heads: int, num_kv_heads: int, head_dim: int, scale: float, window: int = 0) -> None:
+    """out[t, h] = softmax(scale * q[t, h] . K[slot_t, lo..pos_t]) V over the paged cache."""
+    _cuda(q, out, k_cache, v_cache, block_table, positions, token_slot)
+    _i32(positions, "positions"); _i32(token_slot, "token_slot"); _i32(block_table, "block_table")
+    _need(out.is_contiguous() and out.shape[0] >= n_tokens and out.shape[1] == num_heads * head_dim, "attention: out shape")
+    _need(q.dtype == out.dtype == k_cache.dtype == v_cache.dtype, "attention: dtypes differ")
+    _need(k_cache.is_contiguous() and v_cache.is_contiguous()
+          and tuple(k_cache.shape[1:]) == (num_kv_heads, PAGE, head_dim), "attention: cache layout")
+    _need(head_dim % 16 == 0 and head_dim <= 256, f"attention: head_dim {head_dim} must be a multiple of 16 up to 256")
+    _need(num_heads % num_kv_heads == 0, "attention: heads must be a multiple of kv heads")
+    _check(lib("attention_simt").kl_attention_simt(_ptr(q), q_stride, _ptr(out), _ptr(k_cache), _ptr(v_cache),
+                                                   _ptr(block_table), block_table.shape[1], _ptr(positions),
+                                                   _ptr(token_slot), n_tokens, num_heads, num_kv_heads, head_dim,
+                                                   ctypes.c_float(scale), int(window or 0), dtype_code(q.dtype),
+                                                   _stream()), "attention_simt")
+
+
+# --------------------------------------------------------------------------- matrix products
+
+def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out[M, N] = a[M, K] @ w[N, K]^T in plain 32-bit FMA arithmetic; any size."""
+    _cuda(a, w, out)
+    (M, K), (N, K2) = a.shape, w.shape
+    _need(K == K2 and out.shape[0] >= M and out.shape[1] == N, f"gemm: shapes {tuple(a.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)}")
+    _need(a.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1, "gemm: rows must be contiguous")
+    _need(a.dtype == w.dtype, "gemm: operand dtypes differ")
+    _check(lib("gemm_simt").kl_gemm_simt(_ptr(a), a.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0), M, N, K,
+                                         dtype_code(a.dtype), dtype_code(out.dtype), _stream()), "gemm_simt")
+
+
+# --------------------------------------------------------------------------- sampling
+
+def argmax_rows(logits: torch.Tensor, out: torch.Tensor) -> None:
+    _cuda(logits, out)
+    _i32(out, "out")
+    rows, vocab = logits.shape
+    _need(logits.dtype == torch.float32 and logits.stride(1) == 1 and out.numel() >= rows, "argmax: layout")
+    _check(lib("sampling").kl_argmax_rows(_ptr(logits), ctypes.c_longlong(logits.stride(0)), rows, vocab, _ptr(out),
+                                          _stream()), "argmax_rows")
+
+
+def sample_rows(logits: torch.Tensor, temperature: float, top_k: int, seed: int, request_ids: torch.Tensor,
+                steps: torch.Tensor, out: torch.Tensor) -> None:
+    _cuda(logits, request_ids, steps, out)
+    _i32(out, "out"); _i32(request_ids, "request_ids"); _i32(steps, "steps")
+    rows, vocab = logits.shape
+    _need(logits.dtype == torch.float32 and logits.stride(1) == 1, "sample: layout")
+    _need(request_ids.numel() >= rows and steps.numel() >= rows and out.numel() >= rows, "sample: one id and step per row")
+    _need(temperature > 0, "sample: temperature must be positive (0 means argmax)")
+    _check(lib("sampling").kl_sample_rows(_ptr(logits), ctypes.c_longlong(logits.stride(0)), rows, vocab,
+                                          ctypes.c_float(temperature), int(top_k or 0),
+                                          ctypes.c_ulonglong(seed & (2**64 - 1)), _ptr(request_ids), _ptr(steps),
+                                          _ptr(out), _stream()), "sample_rows")
+
+
+# --------------------------------------------------------------------------- dispatch by dtype and shape
+
+def matmul(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out = a @ w^T with the kernel that fits the dtype and the shape.  float32 operands
+    always take the plain 32-bit kernel."""
+    gemm_simt(a, w, out)
+
+
+def attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+              block_table: torch.Tensor, step, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
+              window: int = 0) -> None:
+    """Attention of every token of ``step`` over its sequence's cache."""
+    attention_simt(q, q_stride, out, k_cache, v_cache, block_table, step.positions, step.token_slot, step.n_tokens,
+                   num_heads, num_kv_heads, head_dim, scale, window)

@@ -1,0 +1,113 @@
+// Rotary position encoding fused with the cache write.
+//
+// For every token of the step: rotate its query heads in place, rotate its key heads and
+// store them in the paged cache, and store its value heads unrotated.  Pairs are
+// (j, j + rot/2) inside each head (the half-split layout of HF weights, as
+// ExiledOfCode/KuiperLLama's Llama-3 build rotates them, rope_kernel.cu:5-36; its CPU twin
+// cpu/rope_kernel.cpp:25-41).  The angle is float(position) * inv_freq[j] in 32 bits with
+// sincosf; inv_freq comes from the configuration (theta and scaling are not constants here,
+// unlike rope_kernel.cu:42,128).  Every thread checks its own bounds (the reference guard
+// `idx > total_pairs`, rope_kernel.cu:13, lets one thread past the end).
+#include "common.cuh"
+
+namespace kl {
+
+// qkv: [tokens, (H + 2 KV) * hd], query heads first, then key heads, then value heads.
+template <typename T>
+__global__ void rope_kv_write_kernel(T* __restrict__ qkv, const float* __restrict__ inv_freq, int rot,
+                                     const int* __restrict__ positions, const int* __restrict__ token_slot,
+                                     const int* __restrict__ block_table, int blocks_per_seq,
+                                     T* __restrict__ k_cache, T* __restrict__ v_cache,
+                                     int H, int KV, int hd, int write_kv) {
+    const int t = blockIdx.x;
+    const int slot = token_slot[t];
+    if (slot < 0) return;                                   // a padding row
+    const int pos = positions[t];
+    T* row = qkv + (size_t)t * (H + 2 * KV) * hd;
+    const int half = hd / 2;                                // work items per head: hd/2 pairs of lanes
+    const int rhalf = rot / 2;
+    // queries and keys: (head, j) with j in [0, hd/2): element j and element j + hd/2 are
+    // handled together so that each thread owns what it reads and writes.
+    const int n_qk = (H + KV) * half;
+    for (int idx = threadIdx.x; idx < n_qk; idx += blockDim.x) {
+        const int head = idx / half;
+        const int j = idx - head * half;
+        T* h = row + (size_t)head * hd;
+        // the two elements this thread owns
+        const int e0 = j, e1 = j + half;
+        float v0 = to_f32(h[e0]), v1 = to_f32(h[e1]);
+        if (rot == hd) {
+            float s, c;
+            sincosf((float)pos * inv_freq[j], &s, &c);
+            const float a = v0, b = v1;
+            v0 = a * c - b * s;
+            v1 = b * c + a * s;
+            if (head < H) {
+                h[e0] = from_f32<T>(v0);
+                h[e1] = from_f32<T>(v1);
+            }
+        }
+        if (head >= H && write_kv && rot == hd) {
+            const int g = head - H;
+            T* dst = k_cache + cache_row_offset(block_table, blocks_per_seq, slot, pos, g, KV, hd);
+            dst[e0] = from_f32<T>(v0);
+            dst[e1] = from_f32<T>(v1);
+        }
+    }
+    if (rot != hd) {
+        // Partial or absent rotation: pairs (j, j + rot/2) for j < rot/2; the rest passes through.
+        __syncthreads();
+        const int n_pairs = (H + KV) * rhalf;
+        for (int idx = threadIdx.x; idx < n_pairs; idx += blockDim.x) {
+            const int head = idx / rhalf;
+            const int j = idx - head * rhalf;
+            T* h = row + (size_t)head * hd;
+            float s, c;
+            sincosf((float)pos * inv_freq[j], &s, &c);
+            const float a = to_f32(h[j]), b = to_f32(h[j + rhalf]);
+            h[j] = from_f32<T>(a * c - b * s);
+            h[j + rhalf] = from_f32<T>(b * c + a * s);
+        }
+        __syncthreads();
+        if (write_kv) {
+            for (int idx = threadIdx.x; idx < KV * hd; idx += blockDim.x) {
+                const int g = idx / hd, e = idx - g * hd;
+                T* dst = k_cache + cache_row_offset(block_table, blocks_per_seq, slot, pos, g, KV, hd);
+                dst[e] = row[(size_t)(H + g) * hd + e];
+            }
+        }
+    }
+    if (write_kv) {
+        const T* vsrc = row + (size_t)(H + KV) * hd;
+        for (int idx = threadIdx.x; idx < KV * hd; idx += blockDim.x) {
+            const int g = idx / hd, e = idx - g * hd;
+            T* dst = v_cache + cache_row_offset(block_table, blocks_per_seq, slot, pos, g, KV, hd);
+            dst[e] = vsrc[idx];
+        }
+    }
+}
+
+}  // namespace kl
+
+using namespace kl;
+
+KL_API int kl_rope_kv_write(void* qkv, const float* inv_freq, int rotary_dim, const int* positions,
+                            const int* token_slot, const int* block_table, int blocks_per_seq, void* k_cache,
+                            void* v_cache, int n_tokens, int H, int KV, int hd, int write_kv, int dtype,
+                            cudaStream_t stream) {
+    if (n_tokens <= 0) return KL_OK;
+    if (hd % 2 || rotary_dim % 2 || rotary_dim > hd || rotary_dim < 0) return KL_ERR_BAD_SIZE;
+    if (rotary_dim > 0 && inv_freq == nullptr) return KL_ERR_BAD_SIZE;
+    const int work = (H + KV) * hd / 2;
+    const int threads = work >= 1024 ? 256 : (work >= 256 ? 128 : 64);
+    if (dtype == KL_F32)
+        rope_kv_write_kernel<float><<<n_tokens, threads, 0, stream>>>((float*)qkv, inv_freq, rotary_dim, positions,
+            token_slot, block_table, blocks_per_seq, (float*)k_cache, (float*)v_cache, H, KV, hd, write_kv);
+    else if (dtype == KL_BF16)
+        rope_kv_write_kernel<bf16><<<n_tokens, threads, 0, stream>>>((bf16*)qkv, inv_freq, rotary_dim, positions,
+            token_slot, block_table, blocks_per_seq, (bf16*)k_cache, (bf16*)v_cache, H, KV, hd, write_kv);
+    else
+        return KL_ERR_BAD_DTYPE;
+    KL_LAUNCH_CHECK();
+    return KL_OK;
+}

@@ -1,0 +1,179 @@
+"""The step function: one batch of sequences through the model, from the cache.
+
+A step brings, for each sequence of the batch, its next tokens: a whole prompt of any
+length at the batch's first step, then one token each.  It runs exactly those tokens as one
+packed batch, appends their keys and values to each sequence's slot, and returns float32
+logits at the wanted places.  (ExiledOfCode/KuiperLLama's counterpart is ``predict`` /
+``forward`` for one token of one sequence, kuiper/source/model/llama3.cpp:641-649,146-166;
+its prompt goes through token by token, demo/main.cpp:18-41.)
+
+``Engine`` owns nothing numeric: it packs the batch, keeps the cache's lengths, and calls the
+model.  Decode steps can be replayed from a CUDA graph (``use_graphs``): same kernels, same
+buffers, launched as one graph per batch size.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from ..cache import CacheError, SequenceCache
+from ..parts.base import StepContext
+from .model import DecoderModel
+
+
+class StepError(ValueError):
+    """A batch the step function refuses (the message says why)."""
+
+
+@dataclass
+class SequenceInput:
+    """One sequence's share of a step: the slot it lives in, its next tokens, and the
+    places among these tokens whose logits are wanted."""
+    slot: int
+    tokens: Sequence[int]
+    want: Sequence[int] = field(default_factory=list)
+
+
+class _Staging:
+    """Pinned host buffers and one device buffer that hold all of a step's integer inputs,
+    so that a step costs one host-to-device copy.  The host side is a small ring: a buffer
+    is written again only after the copy that read it has finished (its event), because the
+    host runs ahead of the device."""
+
+    RING = 4
+
+    def __init__(self, capacity: int, device: torch.device):
+        self.capacity = capacity
+        cuda = device.type == "cuda"
+        self.hosts = [torch.zeros(capacity, dtype=torch.int32, pin_memory=cuda) for _ in range(self.RING)]
+        self.events = [torch.cuda.Event() if cuda else None for _ in range(self.RING)]
+        self.used = [False] * self.RING
+        self.turn = 0
+        self.dev = torch.zeros(capacity, dtype=torch.int32, device=device)
+
+    def upload(self, flat: List[int]) -> torch.Tensor:
+        i = self.turn
+        self.turn = (i + 1) % self.RING
+        if self.used[i] and self.events[i] is not None:
+            self.events[i].synchronize()
+        n = len(flat)
+        self.hosts[i][:n] = torch.tensor(flat, dtype=torch.int32)
+        self.dev[:n].copy_(self.hosts[i][:n], non_blocking=True)
+        if self.events[i] is not None:
+            self.events[i].record()
+            self.used[i] = True
+        return self.dev
+
+
+class Engine:
+    def __init__(self, model: DecoderModel, cache: SequenceCache, use_graphs: bool = False):
+        self.model = model
+        self.cache = cache
+        self.device = model.runtime.device
+        self.use_graphs = use_graphs
+        self._staging: Optional[_Staging] = None
+        self._graphs: Dict[int, "_DecodeGraph"] = {}
+        self.launch_log: Optional[List[str]] = None
+
+    # ------------------------------------------------------------------ slots
+    def alloc_slot(self) -> int:
+        return self.cache.alloc_slot()
+
+    def free_slot(self, slot: int) -> None:
+        self.cache.free_slot(slot)
+
+    # ------------------------------------------------------------------ packing
+    def _pack(self, inputs: Sequence[SequenceInput], pad_rows: int) -> Tuple[StepContext, torch.Tensor, int]:
+        if not inputs:
+            raise StepError("an empty batch")
+        vocab = self.model.spec.vocab_size
+        slots, starts, news = [], [], []
+        seen = set()
+        for s in inputs:
+            if not self.cache.slots.is_held(s.slot):
+                raise StepError(f"slot {s.slot} is not held by a sequence")
+            if s.slot in seen:
+                raise StepError(f"slot {s.slot} appears twice in one step")
+            seen.add(s.slot)
+            n = len(s.tokens)
+            if n < 1:
+                raise StepError(f"the sequence in slot {s.slot} brings no token")
+            for w in s.want:
+                if not 0 <= w < n:
+                    raise StepError(f"slot {s.slot}: wanted place {w} is outside its {n} tokens")
+            lo, hi = min(s.tokens), max(s.tokens)
+            if lo < 0 or hi >= vocab:
+                raise StepError(f"slot {s.slot}: token id {lo if lo < 0 else hi} is outside the vocabulary of {vocab}")
+            slots.append(s.slot)
+            starts.append(self.cache.lengths[s.slot])
+            news.append(n)
+        n_real = sum(news)
+        n_rows = n_real + pad_rows
+        n_seqs = len(inputs)
+        n_want = sum(len(s.want) for s in inputs)
+        for s, st, n in zip(inputs, starts, news):
+            try:
+                self.cache.reserve(s.slot, st + n)
+            except CacheError as e:
+                raise StepError(str(e)) from None
+        self.cache.flush_tables()
+
+        # layout of the staging buffer: ids | positions | token_slot | slots | starts | news | cu | want
+        total = 3 * n_rows + 3 * n_seqs + (n_seqs + 1) + n_want
+        if self._staging is None or self._staging.capacity < total:
+            self._staging = _Staging(max(total * 2, 4096), self.device)
+        ids, pos, tsl, cu, want = [], [], [], [0], []
+        row = 0
+        for s, st, n in zip(inputs, starts, news):
+            ids.extend(int(t) for t in s.tokens)
+            pos.extend(range(st, st + n))
+            tsl.extend([s.slot] * n)
+            want.extend(row + w for w in s.want)
+            row += n
+            cu.append(row)
+        ids.extend([0] * pad_rows)
+        pos.extend([0] * pad_rows)
+        tsl.extend([-1] * pad_rows)
+        flat = ids + pos + tsl + slots + starts + news + cu + want
+        d = self._staging.upload(flat)
+        o = 0
+
+        def take(k: int) -> torch.Tensor:
+            nonlocal o
+            v = d[o:o + k]
+            o += k
+            return v
+
+        ctx = StepContext(
+            n_tokens=n_rows, n_seqs=n_seqs, token_ids=take(n_rows), positions=take(n_rows), token_slot=take(n_rows),
+            seq_slots=take(n_seqs), seq_starts=take(n_seqs), seq_new=take(n_seqs), cu_tokens=take(n_seqs + 1),
+            is_decode=all(n == 1 for n in news), max_new=max(news),
+            max_context=max(st + n for st, n in zip(starts, news)),
+            host_slots=slots, host_starts=starts, host_new=news)
+        want_rows = take(n_want)
+        return ctx, want_rows, n_want
+
+    # ------------------------------------------------------------------ the step
+    def step(self, inputs: Sequence[SequenceInput], pad_rows: int = 0) -> Optional[torch.Tensor]:
+        """Run one step.  Returns float32 logits [wanted, vocab] in the order of ``inputs``
+        and of each ``want`` (None when nothing is wanted).  ``pad_rows`` appends rows that
+        belong to no sequence; they change no result."""
+        ctx, want_rows, n_want = self._pack(inputs, pad_rows)
+        residual, pending = self.model.hidden_states(ctx, self.cache)
+        for s, st, n in zip(inputs, ctx.host_starts, ctx.host_new):
+            self.cache.lengths[s.slot] = st + n
+        if n_want == 0:
+            return None
+        return self.model.logits(residual, pending, want_rows)
+
+    def decode_step(self, slots: Sequence[int], tokens: Sequence[int]) -> torch.Tensor:
+        """One token for each of the given sequences; logits [len(slots), vocab]."""
+        return self.step([SequenceInput(s, [int(t)], [0]) for s, t in zip(slots, tokens)])
+
+    def check_device_errors(self) -> None:
+        """Synchronises and raises if a kernel flagged a token id outside the vocabulary."""
+        if int(self.model.error_flag.item()):
+            self.model.error_flag.zero_()
+            raise StepError("a token id outside the vocabulary reached the embedding kernel")

@@ -1,0 +1,145 @@
+"""The parts a layer is put together from, their interfaces and their registries.
+
+A part is built from a ``PartSpec`` (its sizes and constants), a tensor-name prefix, the
+loaded tensors and the run's ``Runtime`` (device and compute dtype).  It never sees the
+model's configuration, so no part knows which model it is in.  A new part is a class with
+the interface below, registered under a name with ``register_mixer`` / ``register_feed_forward``
+/ ``register_norm`` / ``register_position`` / ``register_arrangement``; a ``LayerSpec`` then
+names it.
+
+ExiledOfCode/KuiperLLama's counterpart is its op layer (kuiper/include/op/layer.h:25-188):
+layers with stored inputs and outputs wired by the model class, with eps, theta and head
+counts partly compiled in.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Callable, Dict, List, Optional
+
+import torch
+
+from ..cache import CacheView, KVRequest, StateRequest
+from ..config.spec import PartSpec
+from ..weights.loader import TensorDecl
+
+
+@dataclass(frozen=True)
+class Runtime:
+    """Where and in which precision a model runs.  ``dtype`` is float32 (everything in true
+    32-bit arithmetic) or bfloat16 (serving: bfloat16 storage, 32-bit accumulation)."""
+    device: torch.device
+    dtype: torch.dtype
+
+
+@dataclass
+class StepContext:
+    """One step's batch as the parts see it: packed tokens of several sequences.
+
+    ``n_tokens`` rows are real; tensors may be longer (padding rows have token_slot -1 and
+    write nothing).  All tensors are int32 on the device."""
+    n_tokens: int                 # rows the kernels run (real tokens plus padding rows)
+    n_seqs: int
+    token_ids: torch.Tensor       # [n_tokens]
+    positions: torch.Tensor       # [n_tokens] absolute position of each token in its sequence
+    token_slot: torch.Tensor      # [n_tokens] cache slot of each token's sequence, -1 for padding
+    seq_slots: torch.Tensor       # [n_seqs]
+    seq_starts: torch.Tensor      # [n_seqs] tokens the sequence held before this step
+    seq_new: torch.Tensor         # [n_seqs] tokens of the sequence in this step
+    cu_tokens: torch.Tensor       # [n_seqs + 1] first row of each sequence in the packed batch
+    is_decode: bool               # every sequence brings exactly one token
+    max_new: int                  # host copy: longest run of new tokens
+    max_context: int              # host copy: longest sequence after this step
+    host_slots: List[int]         # host copies for parts that plan their launches
+    host_starts: List[int]
+    host_new: List[int]
+
+
+class Part:
+    """Base of all parts."""
+
+    @classmethod
+    def manifest(cls, spec: PartSpec, prefix: str) -> Dict[str, TensorDecl]:
+        """The tensors the part reads: name -> shape, role and random initialisation."""
+        return {}
+
+    def __init__(self, spec: PartSpec, prefix: str, tensors: Dict[str, torch.Tensor], runtime: Runtime):
+        self.spec = spec
+        self.prefix = prefix
+        self.runtime = runtime
+
+
+class Norm(Part):
+    """``forward(residual, delta, out_rows)``: adds ``delta`` (may be None) to the float32
+    residual stream in place and returns the normalised rows in the compute dtype.  With
+    ``rows`` only those rows are produced and the residual is left unchanged."""
+
+    def forward(self, residual: torch.Tensor, delta: Optional[torch.Tensor], n_rows: int,
+                rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    """A position encoding either rotates queries and keys inside the mixer (``rotary()``
+    returns the inverse frequencies and the rotated width) or changes the embeddings before
+    the first layer (``add_to_embeddings``), or both."""
+
+    def rotary(self) -> Optional[tuple]:
+        return None
+
+    def add_to_embeddings(self, residual: torch.Tensor, step: StepContext) -> None:
+        return None
+
+
+class Mixer(Part):
+    """Mixes information between the tokens of a sequence.  ``kv_request`` / ``state_request``
+    say what the cache must hold for one execution; ``forward`` gets the normalised rows
+    [n_tokens, hidden], the step and its view of the cache, and returns [n_tokens, hidden]
+    in the compute dtype (the block adds it to the residual stream)."""
+
+    def __init__(self, spec, prefix, tensors, runtime, position: Optional[PositionEncoding] = None):
+        super().__init__(spec, prefix, tensors, runtime)
+        self.position = position
+
+    def kv_request(self) -> Optional[KVRequest]:
+        return None
+
+    def state_request(self) -> Optional[StateRequest]:
+        return None
+
+    def forward(self, x: torch.Tensor, step: StepContext, cache: CacheView) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    """``forward(x, step)``: [n_tokens, hidden] -> [n_tokens, hidden], token by token."""
+
+    def forward(self, x: torch.Tensor, step: StepContext) -> torch.Tensor:
+        raise NotImplementedError
+
+
+# ----------------------------------------------------------------------------- registries
+
+_REGISTRIES: Dict[str, Dict[str, type]] = {"mixer": {}, "feed_forward": {}, "norm": {}, "position": {},
+                                           "arrangement": {}}
+
+
+def _register(family: str, name: str) -> Callable[[type], type]:
+    def deco(cls: type) -> type:
+        _REGISTRIES[family][name] = cls
+        return cls
+    return deco
+
+
+def register_mixer(name: str): return _register("mixer", name)
+def register_feed_forward(name: str): return _register("feed_forward", name)
+def register_norm(name: str): return _register("norm", name)
+def register_position(name: str): return _register("position", name)
+def register_arrangement(name: str): return _register("arrangement", name)
+
+
+def part_class(family: str, name: str) -> type:
+    try:
+        return _REGISTRIES[family][name]
+    except KeyError:
+        known = ", ".join(sorted(_REGISTRIES[family])) or "(none)"
+        raise KeyError(f"no {family} is registered as {name!r}; registered: {known}") from None

@@ -1,0 +1,41 @@
+"""The dense SwiGLU feed-forward."""
+from __future__ import annotations
+
+from typing import Dict
+
+import torch
+
+from ..config.spec import PartSpec
+from ..csrc import ops
+from ..weights.loader import TensorDecl
+from .base import FeedForward, Runtime, StepContext, register_feed_forward
+from .linear import Linear
+
+
+@register_feed_forward("swiglu")
+class SwiGLUFeedForward(FeedForward):
+    """f = W_down (silu(W_gate n) * W_up n), silu(g) = g / (1 + exp(-g)), no bias
+    (ExiledOfCode/KuiperLLama kuiper/source/model/llama3.cpp:692-718, swiglu_kernel.cu:18-21;
+    gate = w1, up = w3, down = w2, tools/export_llama3.py:583-585).  Gate and up are stacked
+    into one matrix at load.  Spec: ``hidden_size``, ``intermediate_size``, ``names``."""
+
+    @classmethod
+    def manifest(cls, spec: PartSpec, prefix: str) -> Dict[str, TensorDecl]:
+        hid, inter, n = spec["hidden_size"], spec["intermediate_size"], spec["names"]
+        return {prefix + n["gate"]: TensorDecl((inter, hid)), prefix + n["up"]: TensorDecl((inter, hid)),
+                prefix + n["down"]: TensorDecl((hid, inter))}
+
+    def __init__(self, spec, prefix, tensors, runtime: Runtime):
+        super().__init__(spec, prefix, tensors, runtime)
+        self.hidden, self.inter = int(spec["hidden_size"]), int(spec["intermediate_size"])
+        n = spec["names"]
+        dev, dt = runtime.device, runtime.dtype
+        stacked = torch.cat([tensors[prefix + n[k]].to(device=dev, dtype=dt) for k in ("gate", "up")], dim=0)
+        self.gate_up = Linear(stacked, runtime)
+        self.down = Linear(tensors[prefix + n["down"]], runtime)
+
+    def forward(self, x: torch.Tensor, step: StepContext) -> torch.Tensor:
+        gu = self.gate_up.forward(x)
+        act = torch.empty((x.shape[0], self.inter), dtype=self.runtime.dtype, device=x.device)
+        ops.swiglu(gu, act)
+        return self.down.forward(act)

@@ -1,0 +1,89 @@
+"""Shared by the tests: the tiny configurations, model folders, and the oracle's logits."""
+from __future__ import annotations
+
+import functools
+import json
+import os
+from typing import Dict, List, Sequence
+
+import torch
+
+import plain_llama
+
+# Two tiny configurations of the Llama decoder that differ in every size and option, and a
+# third with a head size that is not hidden/heads and a long context for decoding tests.
+TINY: Dict[str, dict] = {
+    "tiny1": {   # Llama-2 style: MHA, no rope scaling, untied
+        "architectures": ["LlamaForCausalLM"], "hidden_size": 64, "intermediate_size": 172,
+        "num_hidden_layers": 2, "num_attention_heads": 4, "num_key_value_heads": 4, "vocab_size": 256,
+        "max_position_embeddings": 128, "rms_norm_eps": 1e-5, "rope_theta": 10000.0, "rope_scaling": None,
+        "tie_word_embeddings": False, "hidden_act": "silu", "bos_token_id": 1, "eos_token_id": 2,
+    },
+    "tiny2": {   # Llama-3 style: GQA group 3, llama3 rope scaling, tied, two stop tokens
+        "architectures": ["LlamaForCausalLM"], "hidden_size": 192, "intermediate_size": 512,
+        "num_hidden_layers": 3, "num_attention_heads": 6, "num_key_value_heads": 2, "vocab_size": 384,
+        "max_position_embeddings": 256, "rms_norm_eps": 1e-6, "rope_theta": 500000.0,
+        "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                         "original_max_position_embeddings": 64},
+        "tie_word_embeddings": True, "hidden_act": "silu", "bos_token_id": 5, "eos_token_id": [7, 9],
+    },
+    "tiny3": {   # explicit head_dim (heads * head_dim != hidden), GQA group 4, odd vocabulary, long context
+        "architectures": ["LlamaForCausalLM"], "hidden_size": 320, "intermediate_size": 328,
+        "num_hidden_layers": 2, "num_attention_heads": 8, "num_key_value_heads": 2, "head_dim": 64,
+        "vocab_size": 1003, "max_position_embeddings": 2048, "rms_norm_eps": 3e-6, "rope_theta": 250000.0,
+        "rope_scaling": {"rope_type": "llama3", "factor": 4.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                         "original_max_position_embeddings": 512},
+        "tie_word_embeddings": False, "hidden_act": "silu", "eos_token_id": 3,
+    },
+}
+
+
+def config_dict(name: str, **overrides) -> dict:
+    d = json.loads(json.dumps(TINY[name]))
+    d.update(overrides)
+    return d
+
+
+def write_folder(folder: str, name: str, seed: int, **overrides) -> None:
+    """A model folder of random weights through the package's random-weights mode."""
+    from kuiperllama_b200.config import config_from_dict
+    from kuiperllama_b200.engine import write_random_model_folder
+    write_random_model_folder(folder, config_from_dict(config_dict(name, **overrides)), seed)
+
+
+def random_tokens(n: int, vocab: int, seed: int) -> List[int]:
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(0, vocab, (n,), generator=g).tolist()
+
+
+@functools.lru_cache(maxsize=64)
+def _plain_cached(folder: str, tokens: tuple) -> torch.Tensor:
+    c = plain_llama.read_config(folder)
+    w = plain_llama.read_weights(folder)
+    return plain_llama.forward_logits(w, c, list(tokens))
+
+
+def plain_logits(folder: str, tokens: Sequence[int]) -> torch.Tensor:
+    """Logits [T, vocab] of the whole sequence from the plain implementation."""
+    return _plain_cached(folder, tuple(int(t) for t in tokens))
+
+
+# Tolerances, fixed before any kernel was run: float32 paths differ from the oracle only by
+# the order of sums; bfloat16 rounds every activation to 8 bits of mantissa (2^-9 relative)
+# a few dozen times on the way to the logits.
+def tolerance(dtype: str, ref: torch.Tensor) -> float:
+    scale = float(ref.abs().max())
+    return {"float32": 2e-5, "bfloat16": 3e-2}[dtype] * scale + 1e-6
+
+
+def assert_close(got: torch.Tensor, ref: torch.Tensor, dtype: str, what: str = "") -> None:
+    got = got.detach().float().cpu()
+    ref = ref.detach().float().cpu()
+    assert got.shape == ref.shape, f"{what}: shape {tuple(got.shape)} vs {tuple(ref.shape)}"
+    assert torch.isfinite(got).all(), f"{what}: non-finite values"
+    err = (got - ref).abs()
+    tol = tolerance(dtype, ref)
+    if float(err.max()) > tol:
+        idx = int(err.reshape(err.shape[0], -1).max(dim=1).values.argmax()) if err.dim() > 1 else int(err.argmax())
+        raise AssertionError(f"{what}: max abs error {float(err.max()):.3e} > {tol:.3e} "
+                             f"(first axis index of the worst row: {idx}, scale {float(ref.abs().max()):.3e})")

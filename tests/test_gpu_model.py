@@ -1,0 +1,198 @@
+"""The engine against the plain implementation, in float32 and bfloat16: each request alone
+and whole; with its last 32 tokens one by one; in batches of unequal lengths whose shorter
+requests end earlier, one batch after another so that slots and pages are used again; long
+decoding; the first tokens of a sequence; padding rows."""
+from __future__ import annotations
+
+import pytest
+import torch
+
+from helpers import assert_close, config_dict, plain_logits, random_tokens
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = ["float32", "bfloat16"]
+CONFIGS = ["tiny1", "tiny2", "tiny3"]
+
+
+@pytest.fixture(scope="module")
+def engines(model_folders):
+    """(config name, dtype) -> (engine, folder); models are loaded once per module."""
+    from kuiperllama_b200.engine import Engine, load_model
+    made = {}
+
+    def get(name: str, dtype: str, max_tokens: int = 64 * 48):
+        key = (name, dtype)
+        if key not in made:
+            folder = model_folders(name, seed={"tiny1": 0, "tiny2": 1, "tiny3": 2}[name])
+            with torch.inference_mode():
+                model = load_model(folder, dtype=dtype, device="cuda:0")
+                made[key] = (Engine(model, model.new_cache(max_tokens=max_tokens)), folder)
+        return made[key]
+
+    return get
+
+
+def _whole(engine, tokens):
+    from kuiperllama_b200.engine import SequenceInput
+    with torch.inference_mode():
+        slot = engine.alloc_slot()
+        out = engine.step([SequenceInput(slot, tokens, list(range(len(tokens))))])
+        engine.free_slot(slot)
+    return out
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", CONFIGS)
+def test_each_request_alone_and_whole(engines, name, dtype):
+    engine, folder = engines(name, dtype)
+    vocab = config_dict(name)["vocab_size"]
+    for i, n in enumerate([1, 7, 33, 64, 65, 100]):
+        tokens = random_tokens(n, vocab, seed=100 + i)
+        assert_close(_whole(engine, tokens), plain_logits(folder, tokens), dtype, f"{name} whole prompt of {n}")
+    assert engine.cache.slots.held() == 0 and engine.cache.pages_held() == [0]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", CONFIGS)
+def test_last_32_tokens_one_by_one(engines, name, dtype):
+    from kuiperllama_b200.engine import SequenceInput
+    engine, folder = engines(name, dtype)
+    vocab = config_dict(name)["vocab_size"]
+    for n in (33, 90, 127):
+        tokens = random_tokens(n, vocab, seed=200 + n)
+        ref = plain_logits(folder, tokens)
+        head = n - 32
+        with torch.inference_mode():
+            slot = engine.alloc_slot()
+            got = [engine.step([SequenceInput(slot, tokens[:head], list(range(head)))])]
+            for t in range(head, n):
+                got.append(engine.step([SequenceInput(slot, [tokens[t]], [0])]))
+            engine.free_slot(slot)
+        got = torch.cat(got, dim=0)
+        # the first wrong place says what is special about it (a prompt's end, the first decoded token)
+        assert_close(got[:head], ref[:head], dtype, f"{name} prefill part of {n}")
+        assert_close(got[head:head + 1], ref[head:head + 1], dtype, f"{name} first decoded token of {n}")
+        assert_close(got, ref, dtype, f"{name} last 32 one by one of {n}")
+
+
+def _run_batch(engine, requests, prefill_lens):
+    """requests: token lists; prefill_lens[i] tokens go in the first step, the rest one by one.
+    Returns the logits of every position of every request."""
+    from kuiperllama_b200.engine import SequenceInput
+    with torch.inference_mode():
+        slots = [engine.alloc_slot() for _ in requests]
+        out = [[] for _ in requests]
+        logits = engine.step([SequenceInput(s, r[:p], list(range(p))) for s, r, p in zip(slots, requests, prefill_lens)])
+        o = 0
+        for i, p in enumerate(prefill_lens):
+            out[i].append(logits[o:o + p])
+            o += p
+        done = list(prefill_lens)
+        live = [i for i in range(len(requests)) if done[i] < len(requests[i])]
+        for i in range(len(requests)):
+            if i not in live:
+                engine.free_slot(slots[i])
+        while live:
+            logits = engine.step([SequenceInput(slots[i], [requests[i][done[i]]], [0]) for i in live])
+            for j, i in enumerate(live):
+                out[i].append(logits[j:j + 1])
+                done[i] += 1
+            still = []
+            for i in live:
+                if done[i] < len(requests[i]):
+                    still.append(i)
+                else:
+                    engine.free_slot(slots[i])          # a shorter request ends earlier
+            live = still
+    return [torch.cat(o, dim=0) for o in out], slots
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", CONFIGS)
+def test_batches_of_unequal_lengths_reuse_slots(engines, name, dtype):
+    engine, folder = engines(name, dtype)
+    vocab = config_dict(name)["vocab_size"]
+    # (total length, tokens given in the first step); batch after batch on the same slots
+    batches = [[(13, 5), (40, 9), (70, 64), (21, 20)], [(66, 1), (9, 9), (100, 70)], [(120, 65), (64, 33)]]
+    used = []
+    for b, shape in enumerate(batches):
+        requests = [random_tokens(n, vocab, seed=300 + 10 * b + i) for i, (n, _) in enumerate(shape)]
+        got, slots = _run_batch(engine, requests, [p for _, p in shape])
+        used.append(slots)
+        for i, (r, g) in enumerate(zip(requests, got)):
+            ref = plain_logits(folder, r)
+            p = shape[i][1]
+            assert_close(g[:p], ref[:p], dtype, f"{name} batch {b} request {i}: prompt part")
+            assert_close(g, ref, dtype, f"{name} batch {b} request {i}: all positions")
+        assert engine.cache.slots.held() == 0 and engine.cache.pages_held() == [0]
+    assert set(used[1]) & set(used[0]), "the second batch did not reuse a slot of the first"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_decoding(engines, dtype):
+    """A 150-token prompt and 400 tokens one by one across many pages (tiny3, context 2048)."""
+    from kuiperllama_b200.engine import SequenceInput
+    engine, folder = engines("tiny3", dtype)
+    tokens = random_tokens(550, config_dict("tiny3")["vocab_size"], seed=400)
+    ref = plain_logits(folder, tokens)
+    with torch.inference_mode():
+        slot = engine.alloc_slot()
+        got = [engine.step([SequenceInput(slot, tokens[:150], [149])])]
+        for t in range(150, 550):
+            got.append(engine.step([SequenceInput(slot, [tokens[t]], [0])]))
+        engine.free_slot(slot)
+    assert_close(torch.cat(got, dim=0), ref[149:], dtype, "tiny3 long decoding")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", CONFIGS)
+def test_first_tokens_of_a_sequence(engines, name, dtype):
+    """A sequence fed one token at a time from its very first token."""
+    from kuiperllama_b200.engine import SequenceInput
+    engine, folder = engines(name, dtype)
+    tokens = random_tokens(6, config_dict(name)["vocab_size"], seed=500)
+    ref = plain_logits(folder, tokens)
+    with torch.inference_mode():
+        slot = engine.alloc_slot()
+        got = torch.cat([engine.step([SequenceInput(slot, [t], [0])]) for t in tokens], dim=0)
+        engine.free_slot(slot)
+    assert_close(got, ref, dtype, f"{name} first tokens one by one")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_padding_rows_change_nothing(engines, dtype):
+    from kuiperllama_b200.engine import SequenceInput
+    engine, folder = engines("tiny2", dtype)
+    vocab = config_dict("tiny2")["vocab_size"]
+    reqs = [random_tokens(n, vocab, seed=600 + n) for n in (10, 3)]
+    outs = []
+    for pad in (0, 5):
+        with torch.inference_mode():
+            slots = [engine.alloc_slot() for _ in reqs]
+            a = engine.step([SequenceInput(s, r[:-1], list(range(len(r) - 1))) for s, r in zip(slots, reqs)], pad_rows=pad)
+            b = engine.step([SequenceInput(s, [r[-1]], [0]) for s, r in zip(slots, reqs)], pad_rows=pad)
+            for s in slots:
+                engine.free_slot(s)
+        outs.append(torch.cat([a, b], dim=0))
+    assert torch.equal(outs[0], outs[1]), "padding rows changed a logit"
+    ref = torch.cat([plain_logits(folder, r)[:-1] for r in reqs] + [plain_logits(folder, r)[-1:] for r in reqs], dim=0)
+    assert_close(outs[1], ref, dtype, "tiny2 with padding rows")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_logits_do_not_depend_on_the_cut_in_float32_order(engines, dtype):
+    """Whole, split and batched runs of one request agree with each other far inside the
+    tolerance against the oracle: the kernels sum in an order that depends only on the
+    token's own position."""
+    from kuiperllama_b200.engine import SequenceInput
+    engine, folder = engines("tiny2", dtype)
+    vocab = config_dict("tiny2")["vocab_size"]
+    tokens = random_tokens(80, vocab, seed=700)
+    other = random_tokens(45, vocab, seed=701)
+    whole = _whole(engine, tokens)
+    got, _ = _run_batch(engine, [other, tokens], [45, 50])
+    if dtype == "float32":
+        assert torch.equal(got[1], whole), "float32 logits changed with the cut or the batch"
+    else:
+        assert_close(got[1], whole.float().cpu(), "bfloat16", "bf16 cut vs whole")
