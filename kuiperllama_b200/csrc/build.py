@@ -77,7 +77,7 @@ def _writable_dir() -> str:
     for d in _build_dirs():
         try:
             os.makedirs(d, exist_ok=True)
-            probe = os.path.join(d, f".probe-{os.getpid()}")
+            probe = os.path.join(d, f".probe-{os.getpid()}-{threading.get_ident()}")
             with open(probe, "w"):
                 pass
             os.unlink(probe)
