@@ -1,0 +1,121 @@
+"""The generation loop's decisions with a fake backend on the CPU: batches one after another,
+stop tokens, sequences that end earlier, slots handed back and reused."""
+import pytest
+
+from kuiperllama_b200.cache import PAGE
+from kuiperllama_b200.engine.generate import GenerationStats, next_batch, run_requests, tokens_held
+
+
+class FakeBackend:
+    """The next token of a sequence is (sum of its tokens + its length) mod 50."""
+
+    def __init__(self, n_slots):
+        self.free = list(range(n_slots))[::-1]
+        self.held = {}
+        self.log = []
+        self.max_live = 0
+
+    def alloc_slot(self):
+        s = self.free.pop()
+        self.held[s] = None
+        self.max_live = max(self.max_live, len(self.held))
+        return s
+
+    def free_slot(self, slot):
+        assert slot in self.held, "slot freed twice"
+        del self.held[slot]
+        self.free.append(slot)
+        self.log.append(("free", slot))
+
+    @staticmethod
+    def _next(seq):
+        return (sum(seq) + len(seq)) % 50
+
+    def prefill(self, slots, prompts, request_ids):
+        assert len(set(slots)) == len(slots)
+        self.log.append(("prefill", tuple(request_ids), tuple(slots)))
+        out = []
+        for s, p in zip(slots, prompts):
+            assert self.held[s] is None, "prefill into a slot that still holds a sequence"
+            self.held[s] = list(p)
+            out.append(self._next(self.held[s]))
+        return out
+
+    def decode(self, slots, last_tokens, request_ids, steps):
+        self.log.append(("decode", tuple(request_ids), tuple(steps)))
+        out = []
+        for s, t in zip(slots, last_tokens):
+            self.held[s].append(t)
+            out.append(self._next(self.held[s]))
+        return out
+
+
+def expected(prompt, max_new, stop=()):
+    seq, new = list(prompt), []
+    for _ in range(max_new):
+        t = FakeBackend._next(seq)
+        if t in stop:
+            return new, "stop"
+        seq.append(t)
+        new.append(t)
+    return new, "length"
+
+
+def test_batches_follow_one_another_and_every_slot_comes_back():
+    prompts = [[i + 1] * (i % 7 + 1) for i in range(11)]
+    be = FakeBackend(4)
+    stats = GenerationStats()
+    res = run_requests(be, prompts, max_new_tokens=6, max_batch=4, stats=stats)
+    assert [r.tokens for r in res] == [expected(p, 6)[0] for p in prompts]
+    assert all(r.finish_reason == "length" for r in res)
+    assert stats.batches == 3 and be.max_live == 4 and not be.held
+    prefills = [e for e in be.log if e[0] == "prefill"]
+    assert [e[1] for e in prefills] == [(0, 1, 2, 3), (4, 5, 6, 7), (8, 9, 10)]
+    assert set(prefills[1][2]) == set(prefills[0][2])              # the second batch reuses the slots
+    assert stats.prefill_tokens == sum(len(p) for p in prompts)
+    assert stats.decode_tokens == 11 * 5
+
+
+def test_stop_tokens_end_a_sequence_early_and_are_left_out():
+    prompts = [[3], [10, 11], [7, 7, 7], [1, 2, 3, 4]]
+    stop = {FakeBackend._next([10, 11]), expected([7, 7, 7], 3)[0][2]}
+    be = FakeBackend(8)
+    res = run_requests(be, prompts, max_new_tokens=9, stop_ids=stop)
+    for p, r in zip(prompts, res):
+        want, why = expected(p, 9, stop)
+        assert r.tokens == want and r.finish_reason == why
+    assert res[1].tokens == [] and res[1].finish_reason == "stop"  # stopped at its first token
+    assert not be.held
+    # the finished sequences left the batch: later decode steps carry fewer requests
+    sizes = [len(e[1]) for e in be.log if e[0] == "decode"]
+    assert sizes[0] < 4 and sizes == sorted(sizes, reverse=True)
+    # its slot came back before the others went on
+    first_free = next(i for i, e in enumerate(be.log) if e[0] == "free")
+    first_decode = next(i for i, e in enumerate(be.log) if e[0] == "decode")
+    assert first_free < first_decode
+    with_stop = run_requests(FakeBackend(8), prompts, max_new_tokens=9, stop_ids=stop, include_stop=True)
+    assert with_stop[1].tokens == [FakeBackend._next([10, 11])]
+
+
+def test_steps_are_counted_per_request_for_the_sampler():
+    be = FakeBackend(4)
+    run_requests(be, [[1], [2]], max_new_tokens=4)
+    assert [e[2] for e in be.log if e[0] == "decode"] == [(1, 1), (2, 2), (3, 3)]
+
+
+def test_cache_limits_shape_the_batches():
+    lens = [10, 100, 64, 65, 1]
+    assert tokens_held(10, 20, 1000) == PAGE and tokens_held(64, 1, 1000) == 2 * PAGE and tokens_held(100, 500, 128) == 128
+    assert next_batch([0, 1, 2, 3, 4], lens, 10, max_batch=8, token_budget=5 * PAGE, max_seq_len=1000) == [0, 1, 2]
+    assert next_batch([3, 4], lens, 10, max_batch=1, token_budget=1 << 20, max_seq_len=1000) == [3]
+    with pytest.raises(ValueError, match="does not fit"):
+        next_batch([1], lens, 10, max_batch=4, token_budget=PAGE, max_seq_len=1000)
+    be = FakeBackend(8)
+    res = run_requests(be, [[1] * 60, [2] * 30], max_new_tokens=50, max_seq_len=64, token_budget=2 * PAGE)
+    assert len(res[0].tokens) == 4 and res[0].finish_reason == "context"     # 60 + 4 fills the cache's limit
+    assert len(res[1].tokens) == 34 and res[1].finish_reason == "context"
+    with pytest.raises(ValueError, match="empty prompt"):
+        run_requests(FakeBackend(1), [[]], 3)
+    with pytest.raises(ValueError, match="no room"):
+        run_requests(FakeBackend(1), [[1] * 64], 3, max_seq_len=64)
+    assert run_requests(FakeBackend(1), [[1]], 0)[0].tokens == []
