@@ -1,0 +1,136 @@
+"""Generation through the Python entry point and the command line against the plain
+implementation: greedy tokens, temperature and top-k draws, stop tokens, more requests than
+fit in one batch."""
+from __future__ import annotations
+
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+import plain_llama
+from helpers import config_dict, random_tokens, tolerance
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _check_greedy(folder, dtype, prompt, got, stop=()):
+    """Every generated token is the plain implementation's greedy token, unless the plain
+    logits' two best are closer than the dtype's tolerance (then either may win)."""
+    c, w = plain_llama.read_config(folder), plain_llama.read_weights(folder)
+    seq = list(prompt)
+    for tok in got:
+        logits = plain_llama.forward_logits(w, c, seq)[-1]
+        best = plain_llama.argmax_token(logits)
+        if tok != best:
+            assert float(logits[best] - logits[tok]) <= 2 * tolerance(dtype, logits), (dtype, len(seq), tok, best)
+        assert tok not in stop
+        seq.append(tok)
+    return seq
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name,seed", [("tiny1", 0), ("tiny2", 1)])
+def test_greedy_generation_through_the_entry_point(model_folders, name, seed, dtype):
+    import kuiperllama_b200 as kl
+    folder = model_folders(name, seed=seed)
+    vocab = config_dict(name)["vocab_size"]
+    lens = [5, 9, 13] if name == "tiny1" else [1, 7, 20, 33]          # the workloads of the two tiny configurations
+    prompts = [random_tokens(n, vocab, seed=10 * n) for n in lens]
+    m = kl.load(folder, dtype=dtype, max_tokens=64 * 8, max_batch=8)
+    out = m.generate(prompts, max_new_tokens=12, stop_ids=[])
+    assert [len(o) for o in out] == [12] * len(prompts)
+    for p, o in zip(prompts, out):
+        _check_greedy(folder, dtype, p, o)
+    if dtype == "float32":
+        c, w = plain_llama.read_config(folder), plain_llama.read_weights(folder)
+        assert out[1] == plain_llama.greedy_generate(w, c, prompts[1], 12)
+    assert m.cache.slots.held() == 0 and m.cache.pages_held() == [0]
+    assert m.generate(prompts[0], max_new_tokens=3, stop_ids=[]) == out[0][:3]     # a single prompt, not nested
+
+
+def test_stop_tokens_and_more_requests_than_the_cache_holds(model_folders):
+    import kuiperllama_b200 as kl
+    folder = model_folders("tiny2", seed=1)
+    vocab = config_dict("tiny2")["vocab_size"]
+    prompts = [random_tokens(3 + (7 * i) % 40, vocab, seed=900 + i) for i in range(10)]
+    m = kl.load(folder, dtype="float32", max_tokens=64 * 3, max_batch=4)          # three pages: three requests at a time
+    free = m.generate(prompts, max_new_tokens=10, stop_ids=[])
+    assert m.last_stats.batches == 4
+    # make the 4th token of request 2 and the 1st of request 5 stop tokens
+    stop = [free[2][3], free[5][0]]
+    got = m.generate(prompts, max_new_tokens=10, stop_ids=stop)
+    for i, (f, g) in enumerate(zip(free, got)):
+        cut = next((j for j, t in enumerate(f) if t in stop), len(f))
+        assert g == f[:cut], f"request {i}"
+        assert m.last_results[i].finish_reason == ("stop" if cut < len(f) else "length")
+    assert got[5] == [] and len(got[2]) <= 3
+    assert m.cache.slots.held() == 0 and m.cache.pages_held() == [0]
+    # the configuration's own eos ids (7 and 9) are the default stop set
+    assert m.stop_token_ids == (7, 9)
+    assert m.generate(prompts, max_new_tokens=10, stop_ids=stop, include_stop=True)[5] == [free[5][0]]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_temperature_sampling_follows_the_counter_draw(model_folders, dtype):
+    """12 steps at temperature 0.8 with a seeded sampler (the workload of the second tiny
+    configuration): every drawn token's interval of the plain cumulative distribution holds
+    the draw of (seed, request, step); batch of four and one by one give the same tokens."""
+    import kuiperllama_b200 as kl
+    folder = model_folders("tiny2", seed=1)
+    c, w = plain_llama.read_config(folder), plain_llama.read_weights(folder)
+    prompts = [random_tokens(n, c["vocab_size"], seed=20 * n) for n in (1, 7, 20, 33)]
+    m = kl.load(folder, dtype=dtype, max_tokens=64 * 8)
+    out = m.generate(prompts, max_new_tokens=12, temperature=0.8, seed=77, stop_ids=[])
+    slack = {"float32": 1e-4, "bfloat16": 3e-2}[dtype]
+    for r, (p, o) in enumerate(zip(prompts, out)):
+        seq = list(p)
+        for step, tok in enumerate(o):
+            probs = plain_llama.temperature_probabilities(plain_llama.forward_logits(w, c, seq)[-1], 0.8)
+            u = plain_llama.uniform_from_counter(77, r, step)
+            cdf = torch.cumsum(probs, 0)
+            lo = float(cdf[tok - 1]) if tok else 0.0
+            assert lo - slack <= u <= float(cdf[tok]) + slack, (dtype, r, step, tok, u, lo, float(cdf[tok]))
+            seq.append(tok)
+    assert out != m.generate(prompts, max_new_tokens=12, temperature=0.8, seed=78, stop_ids=[])
+    if dtype == "float32":
+        assert m.generate(prompts, max_new_tokens=12, temperature=0.8, seed=77, stop_ids=[]) == out
+        # request 2 alone, told that it is request 2: the same tokens as inside the batch
+        from kuiperllama_b200.engine import EngineBackend, run_requests
+        from kuiperllama_b200.sampling import Sampler, SamplingParams
+        be = EngineBackend(m.engine, Sampler(SamplingParams(temperature=0.8, seed=77)))
+
+        class Shift:
+            def __getattr__(self, k): return getattr(be, k)
+            def prefill(self, s, p, ids): return be.prefill(s, p, [2])
+            def decode(self, s, t, ids, st): return be.decode(s, t, [2], st)
+        with torch.inference_mode():
+            alone = run_requests(Shift(), [prompts[2]], 12)
+        assert alone[0].tokens == out[2]
+    topk = m.generate(prompts, max_new_tokens=6, temperature=1.5, top_k=3, seed=5, stop_ids=[])
+    for p, o in zip(prompts, topk):
+        seq = list(p)
+        for tok in o:
+            logits = plain_llama.forward_logits(w, c, seq)[-1]
+            third = float(torch.topk(logits, 3).values[-1])
+            assert float(logits[tok]) >= third - 2 * tolerance(dtype, logits)
+            seq.append(tok)
+
+
+def test_command_line(model_folders):
+    folder = model_folders("tiny1", seed=0)
+    cmd = [sys.executable, os.path.join(ROOT, "bin", "llama_infer"), folder, "--prompt-ids", "1,5,9,200", "--prompt-ids",
+           "7 8", "--steps", "12", "--dtype", "float32"]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    lines = r.stdout.strip().splitlines()
+    assert lines[0] == "Generating..." and any(l.startswith("steps/s:") for l in lines)
+    first = [int(t) for t in lines[1].split()]
+    c, w = plain_llama.read_config(folder), plain_llama.read_weights(folder)
+    # --steps counts positions, prompt included, as the demo does: 12 - 2 + 1 new tokens for the shorter prompt
+    assert len(first) <= 11 and first == plain_llama.greedy_generate(w, c, [1, 5, 9, 200], 11, stop_ids=[2])[:len(first)]
+    bad = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "llama_infer"), folder], capture_output=True, text=True, timeout=600)
+    assert bad.returncode != 0 and "tokenizer" in bad.stderr

@@ -1,0 +1,320 @@
+"""Each kernel alone against a plain PyTorch float32 (or float64) reference of the same
+operation, at sizes other than the engine's tiny models: widths and vocabularies that are
+no power of two, head sizes in steps of 16, several group sizes, scattered cache pages."""
+from __future__ import annotations
+
+import math
+
+import pytest
+import torch
+
+import plain_llama
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+PAGE = 64
+
+
+def _tol(dtype):
+    return {"float32": 1e-5, "bfloat16": 1.6e-2}[dtype]
+
+
+def _close(got, ref, dtype, what, scale=None):
+    got, ref = got.float().cpu(), ref.float().cpu()
+    scale = float(ref.abs().max()) if scale is None else scale
+    err = float((got - ref).abs().max())
+    assert err <= _tol(dtype) * scale + 1e-7, f"{what}: max abs error {err:.3e}, scale {scale:.3e}"
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from kuiperllama_b200.csrc import ops
+    return ops
+
+
+# ----------------------------------------------------------------------------- embedding
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_embedding_gathers_rows_and_flags_bad_ids(ops, dtype):
+    torch.manual_seed(0)
+    table = torch.randn(1003, 96, device=DEV).to(DT[dtype])
+    ids = torch.tensor([5, 1002, 0, 77, 5], dtype=torch.int32, device=DEV)
+    out = torch.full((5, 96), 7.0, device=DEV)
+    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ops.embedding(ids, table, out, flag)
+    assert torch.equal(out, plain_llama.embedding(table.float().cpu(), ids.tolist()).to(DEV)) and int(flag) == 0
+    bad = torch.tensor([3, 1003, -1], dtype=torch.int32, device=DEV)
+    ops.embedding(bad, table, out, flag)
+    assert int(flag) == 1 and torch.equal(out[0], table[3].float()) and float(out[1:3].abs().sum()) == 0.0
+
+
+# ----------------------------------------------------------------------------- norm
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("hidden", [100, 4096, 8200])
+def test_add_rmsnorm(ops, dtype, hidden):
+    torch.manual_seed(1)
+    T, eps = 37, 3e-6
+    resid = torch.randn(T, hidden, device=DEV) * 3
+    delta = (torch.randn(T, hidden, device=DEV)).to(DT[dtype])
+    w = 1 + 0.1 * torch.randn(hidden, device=DEV)
+    out = torch.empty(T, hidden, device=DEV, dtype=DT[dtype])
+    r0 = resid.clone()
+    ops.add_rmsnorm(resid, None, w, out, eps)                                   # no delta: the stream is untouched
+    assert torch.equal(resid, r0)
+    _close(out, plain_llama.rmsnorm(r0.cpu(), w.cpu(), eps), dtype, "rmsnorm")
+    ops.add_rmsnorm(resid, delta, w, out, eps)                                  # with delta: written back in float32
+    x = r0 + delta.float()
+    assert torch.equal(resid, x), "the residual sum is not the float32 sum"
+    _close(out, plain_llama.rmsnorm(x.cpu(), w.cpu(), eps), dtype, "add+rmsnorm")
+    rows = torch.tensor([36, 0, 5, 5], dtype=torch.int32, device=DEV)
+    out2 = torch.empty(4, hidden, device=DEV, dtype=DT[dtype])
+    before = resid.clone()
+    ops.add_rmsnorm(resid, delta, w, out2, eps, rows)                           # a few rows, nothing written back
+    assert torch.equal(resid, before)
+    x2 = (before + delta.float())[rows.long()]
+    _close(out2, plain_llama.rmsnorm(x2.cpu(), w.cpu(), eps), dtype, "gathered rows")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_swiglu(ops, dtype):
+    torch.manual_seed(2)
+    T, I = 19, 173
+    gu = (torch.randn(T, 2 * I, device=DEV) * 4).to(DT[dtype])
+    out = torch.empty(T, I, device=DEV, dtype=DT[dtype])
+    ops.swiglu(gu, out)
+    g, u = gu.float()[:, :I], gu.float()[:, I:]
+    _close(out, g * (1 / (1 + torch.exp(-g))) * u, dtype, "swiglu")
+
+
+# ----------------------------------------------------------------------------- matrix product
+
+@pytest.mark.parametrize("dtype,out_dtype", [("float32", "float32"), ("bfloat16", "bfloat16"), ("bfloat16", "float32")])
+@pytest.mark.parametrize("M,N,K", [(1, 1003, 172), (3, 65, 64), (70, 130, 333), (129, 64, 16), (64, 256, 4100)])
+def test_gemm_simt(ops, dtype, out_dtype, M, N, K):
+    torch.manual_seed(3)
+    a = torch.randn(M, K, device=DEV).to(DT[dtype])
+    w = torch.randn(N, K, device=DEV).to(DT[dtype])
+    out = torch.empty(M, N, device=DEV, dtype=DT[out_dtype])
+    ops.gemm_simt(a, w, out)
+    ref = (a.double().cpu() @ w.double().cpu().T)
+    # A true 32-bit product: a reduced-precision matrix mode (tf32) would be off by 1e-3.
+    tol = {"float32": 2e-6, "bfloat16": 8e-3}[out_dtype]
+    err = float((out.double().cpu() - ref).abs().max())
+    assert err <= tol * float(ref.abs().max()), f"gemm {M}x{N}x{K} {dtype}->{out_dtype}: error {err:.3e}"
+
+
+def test_gemm_rows_do_not_depend_on_the_batch(ops):
+    torch.manual_seed(4)
+    a = torch.randn(70, 333, device=DEV)
+    w = torch.randn(130, 333, device=DEV)
+    full = torch.empty(70, 130, device=DEV)
+    ops.gemm_simt(a, w, full)
+    one = torch.empty(1, 130, device=DEV)
+    ops.gemm_simt(a[41:42].contiguous(), w, one)
+    assert torch.equal(one[0], full[41])
+
+
+# ----------------------------------------------------------------------------- rope + cache write, attention
+
+class Paged:
+    """A scattered paged cache for tests: pages are dealt to slots in shuffled order."""
+
+    def __init__(self, n_slots, max_len, KV, hd, dtype, seed=0):
+        self.blocks = (max_len + PAGE - 1) // PAGE
+        n_pages = n_slots * self.blocks + 3
+        g = torch.Generator().manual_seed(seed)
+        perm = torch.randperm(n_pages, generator=g)[: n_slots * self.blocks]
+        self.table = perm.view(n_slots, self.blocks).to(torch.int32).to(DEV)
+        # stale contents everywhere: large values that would show if they were read
+        self.k = (torch.randn(n_pages, KV, PAGE, hd, generator=g) * 50).to(dtype).to(DEV)
+        self.v = (torch.randn(n_pages, KV, PAGE, hd, generator=g) * 50).to(dtype).to(DEV)
+
+    def rows(self, which, slot, length):
+        """[length, KV, hd] of a slot, gathered on the host."""
+        t = self.table[slot].tolist()
+        src = (self.k if which == "k" else self.v).float().cpu()
+        return torch.stack([src[t[p // PAGE], :, p % PAGE, :] for p in range(length)], dim=0)
+
+
+def _ref_rope(x, positions, inv_freq, rot):
+    """x [T, heads, hd]: rotate the first `rot` elements of every head, half-split pairs."""
+    if rot == 0:
+        return x.clone()
+    out = x.clone()
+    out[..., :rot] = plain_llama.rope_rotate(x[..., :rot], positions, inv_freq)
+    return out
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H,KV,hd,rot", [(4, 4, 16, 16), (6, 2, 32, 32), (8, 2, 128, 128), (5, 1, 48, 24), (3, 3, 80, 0)])
+def test_rope_kv_write(ops, dtype, H, KV, hd, rot):
+    torch.manual_seed(5)
+    dt = DT[dtype]
+    lens = [70, 1, 130]                                           # tokens of three sequences, appended at offsets
+    starts = [60, 0, 3]
+    cache = Paged(4, 256, KV, hd, dt, seed=1)
+    slots = [2, 0, 3]
+    T = sum(lens)
+    qkv = torch.randn(T, (H + 2 * KV) * hd, device=DEV).to(dt)
+    pos = torch.tensor([s + i for s, n in zip(starts, lens) for i in range(n)], dtype=torch.int32, device=DEV)
+    tslot = torch.tensor([sl for sl, n in zip(slots, lens) for _ in range(n)], dtype=torch.int32, device=DEV)
+    # padding rows: slot -1 must write nothing and leave q alone
+    qkv = torch.cat([qkv, torch.ones(2, qkv.shape[1], device=DEV, dtype=dt)])
+    pos = torch.cat([pos, torch.zeros(2, dtype=torch.int32, device=DEV)])
+    tslot = torch.cat([tslot, torch.full((2,), -1, dtype=torch.int32, device=DEV)])
+    inv = plain_llama.rope_inverse_frequencies(rot, 500000.0, None).to(DEV) if rot else None
+    before_k, before_v = cache.k.clone(), cache.v.clone()
+    x = qkv.clone()
+    ops.rope_kv_write(x, inv, rot, pos, tslot, cache.table, cache.k, cache.v, H, KV, hd)
+    src = qkv[:T].float().cpu().view(T, H + 2 * KV, hd)
+    p = pos[:T].cpu()
+    invc = inv.cpu() if rot else None
+    q_ref = _ref_rope(src[:, :H], p, invc, rot)
+    k_ref = _ref_rope(src[:, H:H + KV], p, invc, rot)
+    v_ref = src[:, H + KV:]
+    _close(x[:T].view(T, H + 2 * KV, hd)[:, :H], q_ref, dtype, "rotated q", scale=float(src.abs().max()))
+    assert torch.equal(x[T:], qkv[T:]), "a padding row was touched"
+    o = 0
+    written = torch.zeros_like(cache.k, dtype=torch.bool)
+    for sl, st, n in zip(slots, starts, lens):
+        rows_k, rows_v = cache.rows("k", sl, st + n), cache.rows("v", sl, st + n)
+        _close(rows_k[st:], k_ref[o:o + n], dtype, f"keys of slot {sl}", scale=float(src.abs().max()))
+        assert torch.equal(rows_v[st:], v_ref[o:o + n].to(dt).float()), "values must be stored as they are"
+        for i in range(st, st + n):
+            written[cache.table[sl, i // PAGE], :, i % PAGE, :] = True
+        o += n
+    assert torch.equal(cache.k[~written], before_k[~written]) and torch.equal(cache.v[~written], before_v[~written]), \
+        "something outside the new tokens' rows was written"
+
+
+def _fill_cache(cache, slot, k, v):
+    """k, v: [len, KV, hd] float tensors -> the slot's pages."""
+    t = cache.table[slot].tolist()
+    for p in range(k.shape[0]):
+        cache.k[t[p // PAGE], :, p % PAGE, :] = k[p].to(cache.k.dtype).to(DEV)
+        cache.v[t[p // PAGE], :, p % PAGE, :] = v[p].to(cache.v.dtype).to(DEV)
+
+
+def _ref_attention(q, k, v, pos, scale, window):
+    """q [H, hd] of one token at position pos; k, v [len, KV, hd]."""
+    H, hd = q.shape
+    KV = k.shape[1]
+    lo = max(0, pos - window + 1) if window else 0
+    out = torch.empty(H, hd, dtype=torch.float64)
+    for h in range(H):
+        g = h // (H // KV)
+        s = (k[lo:pos + 1, g].double() @ q[h].double()) * scale
+        p = torch.softmax(s, dim=0)
+        out[h] = p @ v[lo:pos + 1, g].double()
+    return out
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H,KV,hd,window", [(4, 4, 16, 0), (6, 2, 32, 0), (8, 2, 128, 0), (3, 1, 48, 0), (4, 2, 80, 0),
+                                            (2, 1, 256, 0), (4, 2, 64, 37), (12, 4, 96, 0)])
+def test_attention_simt(ops, dtype, H, KV, hd, window):
+    torch.manual_seed(6)
+    dt = DT[dtype]
+    lens = [200, 1, 65, 129]
+    cache = Paged(5, 256, KV, hd, dt, seed=2)
+    slots = [4, 1, 0, 2]
+    ks = [torch.randn(n, KV, hd) for n in lens]
+    vs = [torch.randn(n, KV, hd) for n in lens]
+    for sl, k, v in zip(slots, ks, vs):
+        _fill_cache(cache, sl, k, v)
+    # query tokens: several positions of every sequence, in one packed batch, plus a padding row
+    picks = [(0, 199), (0, 0), (0, 63), (0, 64), (1, 0), (2, 64), (2, 31), (3, 128), (3, 127), (0, 100)]
+    T = len(picks)
+    scale = 1.0 / math.sqrt(hd)
+    stride = H * hd + 24                                            # q rows inside a wider buffer
+    qbuf = torch.randn(T + 1, stride, device=DEV).to(dt)
+    pos = torch.tensor([p for _, p in picks] + [0], dtype=torch.int32, device=DEV)
+    tslot = torch.tensor([slots[i] for i, _ in picks] + [-1], dtype=torch.int32, device=DEV)
+    out = torch.full((T + 1, H * hd), 3.0, device=DEV, dtype=dt)
+    ops.attention_simt(qbuf, stride, out, cache.k, cache.v, cache.table, pos, tslot, T + 1, H, KV, hd, scale, window)
+    assert float((out[T].float() - 3.0).abs().max()) == 0.0, "a padding row was written"
+    for t, (i, p) in enumerate(picks):
+        q = qbuf[t, :H * hd].float().cpu().view(H, hd)
+        kk = ks[i].to(dt).float()
+        vv = vs[i].to(dt).float()
+        ref = _ref_attention(q, kk, vv, p, scale, window)
+        _close(out[t].view(H, hd), ref, dtype, f"attention token {t} (seq {i}, pos {p})", scale=float(vv.abs().max()))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_attention_finds_one_far_key_among_hundreds(ops, dtype):
+    """One key far back is made to dominate the softmax; the output must be its value.  A
+    kernel that skips a chunk, misreads a page or stops early returns something else."""
+    torch.manual_seed(7)
+    dt = DT[dtype]
+    H, KV, hd, n = 4, 2, 64, 900
+    cache = Paged(2, 1024, KV, hd, dt, seed=3)
+    k = torch.randn(n, KV, hd) * 0.1
+    v = torch.randn(n, KV, hd)
+    q = torch.randn(H, hd) * 0.1
+    for far in (0, 63, 64, 517, 899):
+        kk = k.clone()
+        kk[far, :, :] = 0
+        kk[far, :, 5] = 40.0
+        qq = q.clone()
+        qq[:, 5] = 40.0                                             # score 1600 / 8 = 200 at the far key
+        _fill_cache(cache, 1, kk, v)
+        qbuf = qq.view(1, H * hd).to(dt).to(DEV)
+        out = torch.empty(1, H * hd, device=DEV, dtype=dt)
+        pos = torch.tensor([n - 1], dtype=torch.int32, device=DEV)
+        tslot = torch.tensor([1], dtype=torch.int32, device=DEV)
+        ops.attention_simt(qbuf, H * hd, out, cache.k, cache.v, cache.table, pos, tslot, 1, H, KV, hd, 1 / 8.0, 0)
+        want = v[far].to(dt).float().repeat_interleave(H // KV, dim=0)
+        _close(out.view(H, hd), want, dtype, f"far key at {far}")
+
+
+# ----------------------------------------------------------------------------- sampling
+
+def test_argmax_rows_lowest_index_among_equals(ops):
+    torch.manual_seed(8)
+    logits = torch.randn(7, 128256, device=DEV)
+    logits[2, 99999] = 50.0
+    logits[3, [5, 70000, 128255]] = 60.0                           # equal maxima: the lowest index wins
+    logits[4, 128255] = 70.0
+    out = torch.empty(7, dtype=torch.int32, device=DEV)
+    ops.argmax_rows(logits, out)
+    want = [plain_llama.argmax_token(r) for r in logits.cpu()]
+    assert out.tolist() == want and want[2] == 99999 and want[3] == 5 and want[4] == 128255
+    wide = torch.randn(3, 1003 + 21, device=DEV)[:, :1003]          # rows with a stride
+    out3 = torch.empty(3, dtype=torch.int32, device=DEV)
+    ops.argmax_rows(wide, out3)
+    assert out3.tolist() == wide.argmax(dim=1).tolist()
+
+
+@pytest.mark.parametrize("vocab,temperature,top_k", [(1003, 0.8, 0), (128256, 1.0, 0), (384, 0.5, 5), (5000, 1.3, 50),
+                                                     (777, 2.0, 1)])
+def test_sample_rows_is_the_inverse_cdf_of_the_counter_draw(ops, vocab, temperature, top_k):
+    torch.manual_seed(9)
+    rows, seed = 24, 1234
+    logits = torch.randn(rows, vocab, device=DEV) * 3
+    req = torch.arange(100, 100 + rows, dtype=torch.int32, device=DEV)
+    steps = torch.arange(rows, dtype=torch.int32, device=DEV) % 5
+    out = torch.empty(rows, dtype=torch.int32, device=DEV)
+    ops.sample_rows(logits, temperature, top_k, seed, req, steps, out)
+    again = torch.empty_like(out)
+    ops.sample_rows(logits.clone(), temperature, top_k, seed, req, steps, again)
+    assert torch.equal(out, again)
+    for r in range(rows):
+        p = plain_llama.temperature_probabilities(logits[r].cpu(), temperature, top_k or None)
+        u = plain_llama.uniform_from_counter(seed, int(req[r]), int(steps[r]))
+        c = torch.cumsum(p, 0)
+        got = int(out[r])
+        # the chosen token's interval of the cumulative distribution holds u (up to float rounding)
+        lo = float(c[got - 1]) if got > 0 else 0.0
+        assert float(p[got]) > 0 and lo - 1e-5 <= u <= float(c[got]) + 1e-5, (r, got, u, lo, float(c[got]))
+        if top_k == 1:
+            assert got == plain_llama.argmax_token(logits[r].cpu())
+    # a row's draw depends on its request id and step, not on its place in the batch
+    sub = torch.empty(1, dtype=torch.int32, device=DEV)
+    ops.sample_rows(logits[7:8], temperature, top_k, seed, req[7:8].contiguous(), steps[7:8].contiguous(), sub)
+    assert int(sub) == int(out[7])
+EOF
+echo done
