@@ -316,4 +316,3 @@ def test_sample_rows_is_the_inverse_cdf_of_the_counter_draw(ops, vocab, temperat
     sub = torch.empty(1, dtype=torch.int32, device=DEV)
     ops.sample_rows(logits[7:8], temperature, top_k, seed, req[7:8].contiguous(), steps[7:8].contiguous(), sub)
     assert int(sub) == int(out[7])
-EOF
