@@ -100,8 +100,11 @@ def test_gemm_simt(ops, dtype, out_dtype, M, N, K):
     out = torch.empty(M, N, device=DEV, dtype=DT[out_dtype])
     ops.gemm_simt(a, w, out)
     ref = (a.double().cpu() @ w.double().cpu().T)
-    # A true 32-bit product: a reduced-precision matrix mode (tf32) would be off by 1e-3.
-    tol = {"float32": 2e-6, "bfloat16": 8e-3}[out_dtype]
+    # A true 32-bit product.  A float32 sum of K terms taken one after the other carries a
+    # rounding error of about 2^-24 * sqrt(K) relative to the partial sums; a reduced-precision
+    # matrix mode (tf32: 2^-11 per product) would be off by about 2^-11 * sqrt(K) of one term,
+    # more than ten times the bound below.
+    tol = {"float32": 2.0 * 2.0 ** -24 * math.sqrt(K), "bfloat16": 8e-3}[out_dtype]
     err = float((out.double().cpu() - ref).abs().max())
     assert err <= tol * float(ref.abs().max()), f"gemm {M}x{N}x{K} {dtype}->{out_dtype}: error {err:.3e}"
 
