@@ -50,8 +50,13 @@ def loaded_libraries() -> Dict[str, str]:
     return {n: l._name for n, l in _libs.items()}
 
 
-def _check(code: int, what: str) -> None:
+launch_count = 0       # kernels of this package launched so far (counted per entry-point call)
+
+
+def _check(code: int, what: str, launches: int = 1) -> None:
+    global launch_count
     if code == 0:
+        launch_count += launches
         return
     if code in _ERRORS:
         raise KernelError(f"{what}: {_ERRORS[code]}")
