@@ -1,0 +1,455 @@
+// C = A * W^T in bfloat16 on the fifth-generation tensor cores of sm_100a.
+//
+// Operands are K-major bfloat16 matrices ([rows, K] row-major): TMA (cp.async.bulk.tensor.2d,
+// 128-byte swizzle, no multicast) stages 128 x 64 and BN x 64 tiles in shared memory through
+// a ring of mbarrier-guarded stages; one elected thread issues tcgen05.mma (kind::f16,
+// M = 128, N = BN, K = 16) with the float32 accumulator in tensor memory; four warps read it
+// back with tcgen05.ld and store.  Warp roles: warp 0 loads, warp 1 allocates tensor memory
+// and issues the MMAs, warps 2..5 are the epilogue (their index mod 4 picks the quarter of
+// the 128 tensor-memory lanes that each may read).
+//
+// Two ways of laying a product on the 128 x BN tile:
+//   * tokens as rows (prefill): A = activations [M, K], B = weights [N, K], tile 128 x 256;
+//     out[m, n] in bfloat16 or float32.
+//   * weights as rows (decode, few tokens): A = weights [N, K], B = activations [M <= 64, K],
+//     tile 128 x {16, 32, 64}; the K range may be cut over blockIdx.z, each cut writing
+//     float32 partial sums [z, M, N] that the caller's reduction adds in a fixed order.  Every
+//     weight is read from HBM exactly once per product.
+//
+// This replaces ExiledOfCode/KuiperLLama's matmul_kernel_cu_fp32 (matmul_kernel.cu:6-54), a
+// float32 GEMV with one CTA per output row.  Same contract: y = W x, W [out, in], no bias.
+//
+// Every wait is bounded: a wait that runs out sets a status word that the host reads, the
+// roles stop, the CTA waits (bounded) for its own copies in flight, frees its tensor memory
+// and returns.
+#include "common.cuh"
+#include <cuda.h>
+#include <mutex>
+#include <unordered_map>
+#include <stdio.h>
+
+namespace kl {
+
+constexpr int TC_BM = 128;            // tile rows = UMMA M
+constexpr int TC_BK = 64;             // k per stage: 64 bf16 = one 128-byte swizzle row
+constexpr int TC_THREADS = 192;
+constexpr uint32_t SPIN_LIMIT = 1u << 26;
+
+// ------------------------------------------------------------------------------------------ PTX helpers
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+    return pred != 0;
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false (and raises *abort_flag and *status) when the limit runs out or
+// another role has already given up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int where) {
+    for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 1023u) == 1023u && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    atomicCAS(status, 0, where);
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 : : "r"(smem_u32(dst)), "l"((uint64_t)map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void prefetch_tmap(const CUtensorMap* map) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)map) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 : : "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+// The barrier gets one arrival when all MMAs issued so far by this thread have completed.
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t addr, uint32_t (&r)[32]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(addr));
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t addr, uint32_t (&r)[16]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(addr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 bf16) with
+// the 128-byte swizzle: groups of 8 rows are 1024 bytes apart (stride byte offset), the
+// leading byte offset is unused for swizzled K-major layouts (1), descriptor version 1.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+    return (uint64_t)((addr >> 4) & 0x3FFFu) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
+           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// Instruction descriptor: D float32, A and B bfloat16, both K-major, M = 128, N = n.
+__host__ __device__ constexpr uint32_t umma_idesc(int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+}
+
+// ------------------------------------------------------------------------------------------ the kernel
+
+struct GemmArgs {
+    void* out;          // bf16 or float32
+    long long ld_out;   // elements between rows of out
+    long long split_stride;  // elements between the partial results of two k cuts (weights-as-rows only)
+    int rows_a;         // valid rows of the A operand (tile rows)
+    int rows_b;         // valid rows of the B operand (tile columns)
+    int k_blocks;       // ceil(K / 64)
+    int out_f32;        // 1: float32 output, 0: bfloat16
+    int* status;        // device status word, 0 = fine
+};
+
+template <int BN, int STAGES, bool WEIGHT_ROWS>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmArgs args) {
+    constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2, B_BYTES = BN * TC_BK * 2;
+    constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);     // swizzled tiles want 1024-byte alignment
+    uint8_t* tiles_a = smem;
+    uint8_t* tiles_b = smem + STAGES * A_BYTES;
+    uint64_t* full = (uint64_t*)(tiles_b + STAGES * B_BYTES);
+    uint64_t* empty = full + STAGES;
+    uint64_t* acc_ready = empty + STAGES;
+    uint32_t* tmem_slot = (uint32_t*)(acc_ready + 1);
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile_a = WEIGHT_ROWS ? blockIdx.x : blockIdx.y;          // tile index along the A operand's rows
+    const int tile_b = WEIGHT_ROWS ? 0 : blockIdx.x;
+    // k range of this CTA (cut over blockIdx.z)
+    const int per = (args.k_blocks + gridDim.z - 1) / gridDim.z;
+    const int kb0 = blockIdx.z * per;
+    const int kb1 = min(args.k_blocks, kb0 + per);
+    const int nkb = max(kb1 - kb0, 0);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        mbar_init(acc_ready, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0 && lane == 0) { prefetch_tmap(&map_a); prefetch_tmap(&map_b); }
+    if (warp == 1) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- TMA producer
+        if (elect_one()) {
+            int issued = 0;
+            for (int i = 0; i < nkb; ++i) {
+                const int s = i % STAGES;
+                if (i >= STAGES && !mbar_wait(&empty[s], ((i / STAGES) - 1) & 1, abort_flag, args.status, 1)) break;
+                mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
+                tma_load_2d(tiles_a + s * A_BYTES, &map_a, &full[s], (kb0 + i) * TC_BK, tile_a * TC_BM);
+                tma_load_2d(tiles_b + s * B_BYTES, &map_b, &full[s], (kb0 + i) * TC_BK, tile_b * BN);
+                issued = i + 1;
+            }
+            if (*abort_flag) {
+                // Wait (bounded) for this CTA's own copies in flight before shared memory goes away.
+                for (int i = max(0, issued - STAGES); i < issued; ++i)
+                    for (uint32_t t = 0; t < (1u << 20) && !mbar_try_wait(&full[i % STAGES], (i / STAGES) & 1); ++t) {}
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------- MMA issuer
+        if (elect_one()) {
+            constexpr uint32_t idesc = umma_idesc(BN);
+            bool ok = true;
+            for (int i = 0; i < nkb && ok; ++i) {
+                const int s = i % STAGES;
+                ok = mbar_wait(&full[s], (i / STAGES) & 1, abort_flag, args.status, 2);
+                if (!ok) break;
+                tc_fence_after();
+                const uint64_t da = smem_desc_sw128(smem_u32(tiles_a + s * A_BYTES));
+                const uint64_t db = smem_desc_sw128(smem_u32(tiles_b + s * B_BYTES));
+#pragma unroll
+                for (int k = 0; k < TC_BK / 16; ++k)          // 16 bf16 = 32 bytes along the swizzled row: +2 in 16-byte units
+                    umma_bf16(tmem_base, da + 2 * k, db + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+                umma_commit(&empty[s]);                       // the stage is free once these MMAs have read it
+            }
+            umma_commit(acc_ready);                           // arrives when every MMA above is done (or at once if none)
+        }
+    } else {
+        // ---------------------------------------------------------------- epilogue: warps 2..5
+        const int quarter = warp & 3;                         // the 32 tensor-memory lanes this warp may read
+        const bool ok = mbar_wait(acc_ready, 0, abort_flag, args.status, 3);
+        tc_fence_after();
+        if (ok && !*abort_flag) {
+            const int row = tile_a * TC_BM + quarter * 32 + lane;          // row of the A operand
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+            if constexpr (WEIGHT_ROWS) {
+                // tile rows are output features n, tile columns are tokens m: out[z][m][n]
+                float* out = (float*)args.out + (size_t)blockIdx.z * args.split_stride;
+                __nv_bfloat16* outb = (__nv_bfloat16*)args.out;
+                uint32_t r[16];
+#pragma unroll
+                for (int c = 0; c < BN; c += 16) {
+                    if (nkb > 0) { tmem_ld16(taddr + c, r); tmem_ld_wait(); }
+                    else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) r[j] = 0u;
+                    }
+                    if (row < args.rows_a) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const int m = c + j;
+                            if (m < args.rows_b) {
+                                if (args.out_f32) out[(size_t)m * args.ld_out + row] = __uint_as_float(r[j]);
+                                else outb[(size_t)m * args.ld_out + row] = __float2bfloat16_rn(__uint_as_float(r[j]));
+                            }
+                        }
+                    }
+                }
+            } else {
+                // tile rows are tokens m, tile columns are output features n: out[m][n]
+                uint32_t r[32];
+#pragma unroll 1
+                for (int c = 0; c < BN; c += 32) {
+                    const int n0 = tile_b * BN + c;
+                    if (n0 >= args.rows_b) break;             // uniform across the warp
+                    if (nkb > 0) { tmem_ld32(taddr + c, r); tmem_ld_wait(); }
+                    else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) r[j] = 0u;
+                    }
+                    if (row < args.rows_a) {
+                        const bool full_n = n0 + 32 <= args.rows_b;
+                        if (args.out_f32) {
+                            float* o = (float*)args.out + (size_t)row * args.ld_out + n0;
+                            if (full_n && (args.ld_out & 3) == 0) {
+#pragma unroll
+                                for (int j = 0; j < 32; j += 4)
+                                    *reinterpret_cast<uint4*>(o + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+                            } else {
+                                for (int j = 0; j < 32; ++j)
+                                    if (n0 + j < args.rows_b) o[j] = __uint_as_float(r[j]);
+                            }
+                        } else {
+                            __nv_bfloat16* o = (__nv_bfloat16*)args.out + (size_t)row * args.ld_out + n0;
+                            if (full_n && (args.ld_out & 7) == 0) {
+#pragma unroll
+                                for (int j = 0; j < 32; j += 8) {
+                                    uint4 v;
+                                    __nv_bfloat162 p0 = __floats2bfloat162_rn(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
+                                    __nv_bfloat162 p1 = __floats2bfloat162_rn(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                                    __nv_bfloat162 p2 = __floats2bfloat162_rn(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]));
+                                    __nv_bfloat162 p3 = __floats2bfloat162_rn(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
+                                    v.x = *reinterpret_cast<uint32_t*>(&p0); v.y = *reinterpret_cast<uint32_t*>(&p1);
+                                    v.z = *reinterpret_cast<uint32_t*>(&p2); v.w = *reinterpret_cast<uint32_t*>(&p3);
+                                    *reinterpret_cast<uint4*>(o + j) = v;
+                                }
+                            } else {
+                                for (int j = 0; j < 32; ++j)
+                                    if (n0 + j < args.rows_b) o[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, TMEM_COLS); }
+}
+
+// ------------------------------------------------------------------------------------------ host side
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    });
+    return fn;
+}
+
+struct MapKey {
+    const void* ptr; int rows, cols; long long ld; int box_rows;
+    bool operator==(const MapKey& o) const {
+        return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows;
+    }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        size_t h = (size_t)k.ptr;
+        h = h * 1000003u ^ (size_t)k.rows; h = h * 1000003u ^ (size_t)k.cols;
+        h = h * 1000003u ^ (size_t)k.ld; h = h * 1000003u ^ (size_t)k.box_rows;
+        return h;
+    }
+};
+
+// A tensor map over a [rows, cols] bf16 matrix with `ld` elements between rows; box = 64
+// columns x box_rows rows, 128-byte swizzle, zero fill outside the matrix.  Maps are kept,
+// since weights come back with the same address every step.
+static int make_map(CUtensorMap* out, const void* ptr, int rows, int cols, long long ld, int box_rows) {
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    static std::mutex mu;
+    MapKey key{ptr, rows, cols, ld, box_rows};
+    {
+        std::lock_guard<std::mutex> g(mu);
+        auto it = cache.find(key);
+        if (it != cache.end()) { *out = it->second; return KL_OK; }
+    }
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return KL_ERR_SETUP;
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        fprintf(stderr, "[kuiperllama_b200] cuTensorMapEncodeTiled failed with %d (rows %d cols %d ld %lld box %d)\n", (int)r,
+                rows, cols, ld, box_rows);
+        return KL_ERR_SETUP;
+    }
+    std::lock_guard<std::mutex> g(mu);
+    if (cache.size() > 4096) cache.clear();
+    cache[key] = *out;
+    return KL_OK;
+}
+
+template <int BN, int STAGES, bool WEIGHT_ROWS>
+static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& args, dim3 grid, cudaStream_t stream) {
+    constexpr size_t smem = (size_t)STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + (2 * STAGES + 1) * 8 + 16 + 1024;
+    static bool configured = false;
+    if (!configured) {
+        KL_CUDA(cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, STAGES, WEIGHT_ROWS>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured = true;
+    }
+    gemm_tcgen05_kernel<BN, STAGES, WEIGHT_ROWS><<<grid, TC_THREADS, smem, stream>>>(ma, mb, args);
+    KL_LAUNCH_CHECK();
+    return KL_OK;
+}
+
+static bool aligned_operand(const void* p, long long ld, int K) {
+    return ((uintptr_t)p & 15) == 0 && (ld % 8) == 0 && (K % 8) == 0 && K > 0;
+}
+
+}  // namespace kl
+
+using namespace kl;
+
+// out[M, N] = a[M, K] * w[N, K]^T, tokens as tile rows (any M).  out is bf16 (out_f32 = 0) or
+// float32.  Needs 16-byte aligned bases and row strides (K % 8 == 0): else KL_ERR_BAD_ALIGN.
+KL_API int kl_gemm_tcgen05(const void* a, long long lda, const void* w, long long ldw, void* out, long long ldo, int M,
+                           int N, int K, int out_f32, int* status, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return KL_OK;
+    if (!aligned_operand(a, lda, K) || !aligned_operand(w, ldw, K)) return KL_ERR_BAD_ALIGN;
+    CUtensorMap ma, mb;
+    int rc;
+    if ((rc = make_map(&ma, a, M, K, lda, TC_BM)) != KL_OK) return rc;
+    if ((rc = make_map(&mb, w, N, K, ldw, 256)) != KL_OK) return rc;
+    GemmArgs args{out, ldo, 0, M, N, (K + TC_BK - 1) / TC_BK, out_f32, status};
+    dim3 grid((N + 255) / 256, (M + TC_BM - 1) / TC_BM, 1);
+    if (grid.y > 65535) return KL_ERR_BAD_SIZE;
+    return launch<256, 4, false>(ma, mb, args, grid, stream);
+}
+
+// Few tokens (M <= 64): weights as tile rows, the K range cut into `splits` pieces.
+// splits == 1: out[M, N] directly (bf16 or float32).  splits > 1: out is float32
+// [splits, M, N] partial sums (out_f32 must be 1) for the caller to add.
+KL_API int kl_gemm_tcgen05_skinny(const void* a, long long lda, const void* w, long long ldw, void* out, long long ldo,
+                                  int M, int N, int K, int splits, int out_f32, int* status, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return KL_OK;
+    if (M > 64) return KL_ERR_BAD_SIZE;
+    if (!aligned_operand(a, lda, K) || !aligned_operand(w, ldw, K)) return KL_ERR_BAD_ALIGN;
+    const int k_blocks = (K + TC_BK - 1) / TC_BK;
+    if (splits < 1 || splits > k_blocks || splits > 65535) return KL_ERR_BAD_SIZE;
+    if (splits > 1 && !out_f32) return KL_ERR_BAD_DTYPE;
+    const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+    CUtensorMap ma, mb;
+    int rc;
+    if ((rc = make_map(&ma, w, N, K, ldw, TC_BM)) != KL_OK) return rc;
+    if ((rc = make_map(&mb, a, M, K, lda, bn)) != KL_OK) return rc;
+    GemmArgs args{out, ldo, (long long)M * ldo, N, M, k_blocks, out_f32, status};
+    dim3 grid((N + TC_BM - 1) / TC_BM, 1, splits);
+    // two CTAs share an SM so that one's epilogue overlaps the other's loads
+    if (bn == 16) return launch<16, 6, true>(ma, mb, args, grid, stream);
+    if (bn == 32) return launch<32, 5, true>(ma, mb, args, grid, stream);
+    return launch<64, 4, true>(ma, mb, args, grid, stream);
+}
+
+namespace kl {
+// out[m, n] = sum over z of partial[z, m, n], added in ascending z.
+template <typename TO>
+__global__ void splitk_reduce_kernel(const float* __restrict__ partial, int splits, int M, int N, TO* __restrict__ out,
+                                     long long ldo) {
+    const size_t total = (size_t)M * N;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        float acc = 0.f;
+        for (int z = 0; z < splits; ++z) acc += partial[(size_t)z * total + i];
+        const size_t m = i / N, n = i - m * N;
+        out[m * ldo + n] = from_f32<TO>(acc);
+    }
+}
+}  // namespace kl
+
+KL_API int kl_splitk_reduce(const float* partial, int splits, int M, int N, void* out, long long ldo, int out_f32,
+                            cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return KL_OK;
+    const size_t total = (size_t)M * N;
+    const int threads = 256;
+    const int blocks = (int)((total + threads - 1) / threads < 148 * 8 ? (total + threads - 1) / threads : 148 * 8);
+    if (out_f32) kl::splitk_reduce_kernel<float><<<blocks, threads, 0, stream>>>(partial, splits, M, N, (float*)out, ldo);
+    else kl::splitk_reduce_kernel<kl::bf16><<<blocks, threads, 0, stream>>>(partial, splits, M, N, (kl::bf16*)out, ldo);
+    KL_LAUNCH_CHECK();
+    return KL_OK;
+}

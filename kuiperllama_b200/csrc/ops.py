@@ -227,10 +227,94 @@ def sample_rows(logits: torch.Tensor, temperature: float, top_k: int, seed: int,
 
 # --------------------------------------------------------------------------- dispatch by dtype and shape
 
+_status_words: Dict[int, torch.Tensor] = {}
+
+
+def status_word(device: torch.device) -> torch.Tensor:
+    """The device's int32 status word: kernels with bounded waits write a non-zero code into it
+    when a wait runs out.  ``check_status`` reads it (that synchronises)."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx not in _status_words:
+        _status_words[idx] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _status_words[idx]
+
+
+def check_status(device: torch.device) -> None:
+    word = status_word(device)
+    code = int(word.item())
+    if code:
+        word.zero_()
+        raise KernelError(f"a tensor-core kernel gave up waiting (code {code}: 1 = loader, 2 = MMA issuer, 3 = epilogue)")
+
+
+def _tc_ok(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
+    """Whether the TMA-fed tensor-core kernels take these operands: bfloat16, rows that start
+    on 16-byte boundaries (K and the row strides multiples of 8 elements)."""
+    K = a.shape[1]
+    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and out.dtype in (torch.bfloat16, torch.float32)
+            and K % 8 == 0 and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and a.stride(1) == 1 and w.stride(1) == 1
+            and out.stride(1) == 1)
+
+
+SM_COUNT = 148
+
+
+def skinny_splits(N: int, K: int) -> int:
+    """Into how many pieces the K range is cut for a product with few tokens, so that about two
+    CTAs per SM stream weights: 128 output features per CTA, at least 4 k-blocks of 64 each."""
+    tiles = (N + 127) // 128
+    k_blocks = (K + 63) // 64
+    want = max(1, min((2 * SM_COUNT + tiles // 2) // tiles, k_blocks // 4, 32))
+    per = (k_blocks + want - 1) // want
+    return (k_blocks + per - 1) // per
+
+
+def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out[M, N] = a @ w^T on the tensor cores, tokens as tile rows (any M)."""
+    _cuda(a, w, out)
+    (M, K), (N, K2) = a.shape, w.shape
+    _need(K == K2 and out.shape[0] >= M and out.shape[1] == N, "gemm_tcgen05: shapes")
+    _need(_tc_ok(a, w, out), "gemm_tcgen05: operands must be bfloat16 with 16-byte aligned rows")
+    _check(lib("gemm_tcgen05").kl_gemm_tcgen05(_ptr(a), ctypes.c_longlong(a.stride(0)), _ptr(w),
+                                               ctypes.c_longlong(w.stride(0)), _ptr(out), ctypes.c_longlong(out.stride(0)),
+                                               M, N, K, int(out.dtype == torch.float32), _ptr(status_word(a.device)),
+                                               _stream()), "gemm_tcgen05")
+
+
+def gemm_skinny(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, splits: Optional[int] = None) -> None:
+    """out[M, N] = a @ w^T for M <= 64 tokens: weights as tile rows, each weight read once, the
+    K range cut into ``splits`` pieces whose float32 partial sums are added in a fixed order."""
+    _cuda(a, w, out)
+    (M, K), (N, K2) = a.shape, w.shape
+    _need(K == K2 and out.shape[0] >= M and out.shape[1] == N and M <= 64, "gemm_skinny: shapes")
+    _need(_tc_ok(a, w, out), "gemm_skinny: operands must be bfloat16 with 16-byte aligned rows")
+    splits = skinny_splits(N, K) if splits is None else splits
+    L = lib("gemm_tcgen05")
+    st = _ptr(status_word(a.device))
+    if splits == 1:
+        _check(L.kl_gemm_tcgen05_skinny(_ptr(a), ctypes.c_longlong(a.stride(0)), _ptr(w), ctypes.c_longlong(w.stride(0)),
+                                        _ptr(out), ctypes.c_longlong(out.stride(0)), M, N, K, 1,
+                                        int(out.dtype == torch.float32), st, _stream()), "gemm_skinny")
+        return
+    partial = torch.empty((splits, M, N), dtype=torch.float32, device=a.device)
+    _check(L.kl_gemm_tcgen05_skinny(_ptr(a), ctypes.c_longlong(a.stride(0)), _ptr(w), ctypes.c_longlong(w.stride(0)),
+                                    _ptr(partial), ctypes.c_longlong(N), M, N, K, splits, 1, st, _stream()), "gemm_skinny")
+    _check(L.kl_splitk_reduce(_ptr(partial), splits, M, N, _ptr(out), ctypes.c_longlong(out.stride(0)),
+                              int(out.dtype == torch.float32), _stream()), "splitk_reduce")
+
+
 def matmul(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
     """out = a @ w^T with the kernel that fits the dtype and the shape.  float32 operands
-    always take the plain 32-bit kernel."""
-    gemm_simt(a, w, out)
+    always take the plain 32-bit kernel; bfloat16 operands take the tensor-core kernels when
+    their rows are 16-byte aligned (few tokens: weights as tile rows), else the plain kernel."""
+    if a.dtype == torch.bfloat16 and _tc_ok(a, w, out):
+        if a.shape[0] <= 64:
+            gemm_skinny(a, w, out)
+        else:
+            gemm_tcgen05(a, w, out)
+    else:
+        gemm_simt(a, w, out)
 
 
 def attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,

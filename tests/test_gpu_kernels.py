@@ -319,3 +319,50 @@ def test_sample_rows_is_the_inverse_cdf_of_the_counter_draw(ops, vocab, temperat
     sub = torch.empty(1, dtype=torch.int32, device=DEV)
     ops.sample_rows(logits[7:8], temperature, top_k, seed, req[7:8].contiguous(), steps[7:8].contiguous(), sub)
     assert int(sub) == int(out[7])
+
+
+# ----------------------------------------------------------------------------- tensor-core products
+
+@pytest.mark.parametrize("out_dtype", ["bfloat16", "float32"])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (65, 72, 136), (300, 1000, 520), (2048, 512, 4096), (129, 257, 72),
+                                   (1000, 130, 1024)])
+def test_gemm_tcgen05(ops, out_dtype, M, N, K):
+    torch.manual_seed(10)
+    a = torch.randn(M, K, device=DEV).bfloat16()
+    w = torch.randn(N, K, device=DEV).bfloat16()
+    out = torch.full((M, N), 7.0, device=DEV, dtype=DT[out_dtype])
+    ops.gemm_tcgen05(a, w, out)
+    ops.check_status(out.device)
+    ref = a.double().cpu() @ w.double().cpu().T
+    tol = {"float32": 2.0 * 2.0 ** -24 * math.sqrt(K), "bfloat16": 8e-3}[out_dtype]
+    err = float((out.double().cpu() - ref).abs().max())
+    assert err <= tol * float(ref.abs().max()), f"tcgen05 gemm {M}x{N}x{K} -> {out_dtype}: error {err:.3e}"
+
+
+@pytest.mark.parametrize("out_dtype", ["bfloat16", "float32"])
+@pytest.mark.parametrize("M,N,K,splits", [(1, 128, 64, 1), (8, 4096, 4096, None), (16, 1000, 520, 3), (17, 130, 1024, 4),
+                                          (33, 257, 72, 2), (64, 6144, 4096, None), (5, 1003, 14336, None), (3, 200, 64, 1)])
+def test_gemm_skinny(ops, out_dtype, M, N, K, splits):
+    torch.manual_seed(11)
+    a = torch.randn(M, K, device=DEV).bfloat16()
+    w = torch.randn(N, K, device=DEV).bfloat16()
+    out = torch.full((M, N), 7.0, device=DEV, dtype=DT[out_dtype])
+    ops.gemm_skinny(a, w, out, splits)
+    ops.check_status(out.device)
+    ref = a.double().cpu() @ w.double().cpu().T
+    tol = {"float32": 2.0 * 2.0 ** -24 * math.sqrt(K), "bfloat16": 8e-3}[out_dtype]
+    err = float((out.double().cpu() - ref).abs().max())
+    assert err <= tol * float(ref.abs().max()), f"skinny gemm {M}x{N}x{K} -> {out_dtype}: error {err:.3e}"
+
+
+def test_matmul_picks_a_kernel_for_every_shape(ops):
+    """Rows that are not 16-byte aligned (K = 172) go to the plain kernel, never to a wrong result."""
+    torch.manual_seed(12)
+    for M, N, K in [(5, 64, 172), (100, 64, 172), (5, 172, 64), (100, 172, 64)]:
+        a = torch.randn(M, K, device=DEV).bfloat16()
+        w = torch.randn(N, K, device=DEV).bfloat16()
+        out = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+        ops.matmul(a, w, out)
+        ref = a.double().cpu() @ w.double().cpu().T
+        assert float((out.double().cpu() - ref).abs().max()) <= 8e-3 * float(ref.abs().max())
+    ops.check_status(torch.device(DEV))
