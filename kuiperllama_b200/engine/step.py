@@ -67,6 +67,15 @@ class _Staging:
         return self.dev
 
 
+class _DecodeGraph:
+    """One captured decode step for a fixed number of sequences.  The kernels read their
+    integer inputs from the engine's staging buffer and the cache's block tables, which keep
+    their addresses; a replay runs the step on whatever those hold."""
+
+    def __init__(self, graph: "torch.cuda.CUDAGraph", logits: torch.Tensor, staging_ptr: int, launches: int):
+        self.graph, self.logits, self.staging_ptr, self.launches = graph, logits, staging_ptr, launches
+
+
 class Engine:
     def __init__(self, model: DecoderModel, cache: SequenceCache, use_graphs: bool = False):
         self.model = model
@@ -74,8 +83,7 @@ class Engine:
         self.device = model.runtime.device
         self.use_graphs = use_graphs
         self._staging: Optional[_Staging] = None
-        self._graphs: Dict[int, "_DecodeGraph"] = {}
-        self.launch_log: Optional[List[str]] = None
+        self._graphs: Dict[int, _DecodeGraph] = {}
 
     # ------------------------------------------------------------------ slots
     def alloc_slot(self) -> int:
@@ -123,7 +131,7 @@ class Engine:
         # layout of the staging buffer: ids | positions | token_slot | slots | starts | news | cu | want
         total = 3 * n_rows + 3 * n_seqs + (n_seqs + 1) + n_want
         if self._staging is None or self._staging.capacity < total:
-            self._staging = _Staging(max(total * 2, 4096), self.device)
+            self._staging = _Staging(max(total * 2, 1 << 16), self.device)
         ids, pos, tsl, cu, want = [], [], [], [0], []
         row = 0
         for s, st, n in zip(inputs, starts, news):
@@ -169,8 +177,43 @@ class Engine:
         return self.model.logits(residual, pending, want_rows)
 
     def decode_step(self, slots: Sequence[int], tokens: Sequence[int]) -> torch.Tensor:
-        """One token for each of the given sequences; logits [len(slots), vocab]."""
-        return self.step([SequenceInput(s, [int(t)], [0]) for s, t in zip(slots, tokens)])
+        """One token for each of the given sequences; logits [len(slots), vocab].
+
+        With ``use_graphs`` the step of a batch size is captured in a CUDA graph the first
+        time it runs and replayed afterwards: the same kernels on the same buffers with one
+        launch.  The logits tensor of a replayed step is the graph's own output buffer; it is
+        overwritten by the next decode step of the same batch size."""
+        inputs = [SequenceInput(s, [int(t)], [0]) for s, t in zip(slots, tokens)]
+        if not self.use_graphs:
+            return self.step(inputs)
+        from ..csrc import ops
+        n = len(inputs)
+        ctx, want_rows, _ = self._pack(inputs, 0)
+        g = self._graphs.get(n)
+        if g is not None and g.staging_ptr != self._staging.dev.data_ptr():
+            self._graphs.clear()                          # the staging buffer moved: captured addresses are stale
+            g = None
+        if g is None:
+            # The first step of this size runs eagerly (it also warms every kernel up); then the
+            # same calls are captured for the steps that follow.  Capturing launches nothing.
+            residual, pending = self.model.hidden_states(ctx, self.cache)
+            logits = self.model.logits(residual, pending, want_rows)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            before = ops.launch_count
+            with torch.cuda.graph(graph):
+                r2, p2 = self.model.hidden_states(ctx, self.cache)
+                static_logits = self.model.logits(r2, p2, want_rows)
+            captured = ops.launch_count - before
+            ops.launch_count = before                     # captured calls are not launches; replays are counted below
+            self._graphs[n] = _DecodeGraph(graph, static_logits, self._staging.dev.data_ptr(), captured)
+        else:
+            g.graph.replay()
+            ops.launch_count += g.launches
+            logits = g.logits
+        for s, st in zip(inputs, ctx.host_starts):
+            self.cache.lengths[s.slot] = st + 1
+        return logits
 
     def check_device_errors(self) -> None:
         """Synchronises and raises if a kernel flagged a token id outside the vocabulary."""

@@ -196,3 +196,37 @@ def test_logits_do_not_depend_on_the_cut_in_float32_order(engines, dtype):
         assert torch.equal(got[1], whole), "float32 logits changed with the cut or the batch"
     else:
         assert_close(got[1], whole.float().cpu(), "bfloat16", "bf16 cut vs whole")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["tiny2", "tiny3"])
+def test_decode_steps_replayed_from_cuda_graphs(model_folders, name, dtype):
+    """The decode step captured in a CUDA graph per batch size: batches shrink as requests end,
+    a later batch reuses slots and graphs, pages are crossed while replaying."""
+    from kuiperllama_b200.engine import Engine, SequenceInput, load_model
+    folder = model_folders(name, seed={"tiny2": 1, "tiny3": 2}[name])
+    vocab = config_dict(name)["vocab_size"]
+    with torch.inference_mode():
+        model = load_model(folder, dtype=dtype, device="cuda:0")
+        engine = Engine(model, model.new_cache(max_tokens=64 * 12), use_graphs=True)
+        for batch in range(2):
+            shape = [(100, 60), (70, 62), (90, 3)]                        # (total, given at first)
+            reqs = [random_tokens(n, vocab, seed=800 + 10 * batch + i) for i, (n, _) in enumerate(shape)]
+            slots = [engine.alloc_slot() for _ in reqs]
+            engine.step([SequenceInput(s, r[:p], []) for s, r, (_, p) in zip(slots, reqs, shape)])
+            done = [p for _, p in shape]
+            live = [0, 1, 2]
+            got = [[] for _ in reqs]
+            while live:
+                logits = engine.decode_step([slots[i] for i in live], [reqs[i][done[i]] for i in live]).clone()
+                for j, i in enumerate(live):
+                    got[i].append(logits[j])
+                    done[i] += 1
+                for i in [i for i in live if done[i] == len(reqs[i])]:
+                    engine.free_slot(slots[i])
+                live = [i for i in live if done[i] < len(reqs[i])]
+            for i, r in enumerate(reqs):
+                assert_close(torch.stack(got[i]), plain_logits(folder, r)[shape[i][1]:], dtype, f"{name} graphs batch {batch} request {i}")
+        assert sorted(engine._graphs) == [1, 2, 3]
+        from kuiperllama_b200.csrc import ops
+        ops.check_status(torch.device("cuda:0"))
