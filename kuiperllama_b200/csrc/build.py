@@ -28,6 +28,7 @@ SOURCES: Dict[str, str] = {
     "rowwise": "rowwise.cu",
     "rope_kv": "rope_kv.cu",
     "attention_simt": "attention_simt.cu",
+    "attention_decode": "attention_decode.cu",
     "gemm_simt": "gemm_simt.cu",
     "gemm_tcgen05": "gemm_tcgen05.cu",
     "sampling": "sampling.cu",

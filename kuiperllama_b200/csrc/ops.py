@@ -317,9 +317,51 @@ def matmul(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
         gemm_simt(a, w, out)
 
 
+DECODE_HEAD_DIMS = (16, 32, 64, 128, 256)
+
+
+def decode_splits(rows: int, num_heads: int, num_kv_heads: int) -> int:
+    """Into how many pieces each sequence's keys are cut in decode attention: enough CTAs for
+    about two per SM, from the batch size alone (never from the lengths, so that a captured
+    graph stays valid while the sequences grow)."""
+    group = num_heads // num_kv_heads
+    tiles = (group + 3) // 4 if group >= 3 else 1
+    ctas = max(1, rows * num_kv_heads * tiles)
+    return max(1, min(32, (2 * SM_COUNT + ctas - 1) // ctas))
+
+
+def attention_decode(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                     block_table: torch.Tensor, positions: torch.Tensor, token_slot: torch.Tensor, rows: int,
+                     num_heads: int, num_kv_heads: int, head_dim: int, scale: float, window: int = 0,
+                     splits: Optional[int] = None) -> None:
+    """One query token per row against its sequence's cache, keys cut over ``splits`` CTAs."""
+    _cuda(q, out, k_cache, v_cache, block_table, positions, token_slot)
+    _i32(positions, "positions"); _i32(token_slot, "token_slot"); _i32(block_table, "block_table")
+    _need(q.dtype == out.dtype == k_cache.dtype == v_cache.dtype == torch.bfloat16, "attention_decode: bfloat16 only")
+    _need(head_dim in DECODE_HEAD_DIMS, f"attention_decode: head_dim {head_dim} not in {DECODE_HEAD_DIMS}")
+    _need(out.is_contiguous() and out.shape[0] >= rows and out.shape[1] == num_heads * head_dim, "attention_decode: out shape")
+    _need(k_cache.is_contiguous() and v_cache.is_contiguous()
+          and tuple(k_cache.shape[1:]) == (num_kv_heads, PAGE, head_dim), "attention_decode: cache layout")
+    _need(num_heads % num_kv_heads == 0, "attention_decode: heads must be a multiple of kv heads")
+    splits = decode_splits(rows, num_heads, num_kv_heads) if splits is None else splits
+    po = pml = None
+    if splits > 1:
+        po = torch.empty((rows, num_heads, splits, head_dim), dtype=torch.float32, device=q.device)
+        pml = torch.empty((rows, num_heads, splits, 2), dtype=torch.float32, device=q.device)
+    _check(lib("attention_decode").kl_attention_decode(
+        _ptr(q), q_stride, _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1],
+        _ptr(positions), _ptr(token_slot), _ptr(po), _ptr(pml), rows, num_heads, num_kv_heads, head_dim,
+        ctypes.c_float(scale), int(window or 0), splits, _stream()), "attention_decode", 2 if splits > 1 else 1)
+
+
 def attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
               block_table: torch.Tensor, step, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
               window: int = 0) -> None:
-    """Attention of every token of ``step`` over its sequence's cache."""
-    attention_simt(q, q_stride, out, k_cache, v_cache, block_table, step.positions, step.token_slot, step.n_tokens,
-                   num_heads, num_kv_heads, head_dim, scale, window)
+    """Attention of every token of ``step`` over its sequence's cache.  bfloat16 decode steps
+    (one token per sequence) take the split-KV kernel; everything else the plain kernel."""
+    if step.is_decode and q.dtype == torch.bfloat16 and head_dim in DECODE_HEAD_DIMS and q_stride % 8 == 0:
+        attention_decode(q, q_stride, out, k_cache, v_cache, block_table, step.positions, step.token_slot, step.n_tokens,
+                         num_heads, num_kv_heads, head_dim, scale, window)
+    else:
+        attention_simt(q, q_stride, out, k_cache, v_cache, block_table, step.positions, step.token_slot, step.n_tokens,
+                       num_heads, num_kv_heads, head_dim, scale, window)

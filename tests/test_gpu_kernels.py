@@ -366,3 +366,57 @@ def test_matmul_picks_a_kernel_for_every_shape(ops):
         ref = a.double().cpu() @ w.double().cpu().T
         assert float((out.double().cpu() - ref).abs().max()) <= 8e-3 * float(ref.abs().max())
     ops.check_status(torch.device(DEV))
+
+
+# ----------------------------------------------------------------------------- split-KV decode attention
+
+@pytest.mark.parametrize("H,KV,hd,window,splits", [(4, 4, 16, 0, 1), (6, 2, 32, 0, 3), (8, 2, 128, 0, None), (32, 8, 128, 0, 5),
+                                                   (3, 1, 64, 0, 2), (16, 2, 64, 0, 4), (2, 1, 256, 0, 7), (4, 2, 64, 37, 3),
+                                                   (8, 8, 128, 100, 32), (5, 5, 32, 0, 32)])
+def test_attention_decode(ops, H, KV, hd, window, splits):
+    torch.manual_seed(13)
+    dt = torch.bfloat16
+    lens = [200, 1, 65, 129, 64, 250]
+    cache = Paged(7, 256, KV, hd, dt, seed=4)
+    slots = [4, 1, 0, 2, 6, 5]
+    ks = [torch.randn(n, KV, hd) for n in lens]
+    vs = [torch.randn(n, KV, hd) for n in lens]
+    for sl, k, v in zip(slots, ks, vs):
+        _fill_cache(cache, sl, k, v)
+    rows = len(lens) + 1                                            # the last token of every sequence, one padding row
+    stride = H * hd + 2 * KV * hd
+    qbuf = torch.randn(rows, stride, device=DEV).to(dt)
+    pos = torch.tensor([n - 1 for n in lens] + [0], dtype=torch.int32, device=DEV)
+    tslot = torch.tensor(slots + [-1], dtype=torch.int32, device=DEV)
+    out = torch.full((rows, H * hd), 3.0, device=DEV, dtype=dt)
+    ops.attention_decode(qbuf, stride, out, cache.k, cache.v, cache.table, pos, tslot, rows, H, KV, hd, 1 / math.sqrt(hd),
+                         window, splits)
+    assert float((out[-1].float() - 3.0).abs().max()) == 0.0, "a padding row was written"
+    for t, n in enumerate(lens):
+        q = qbuf[t, :H * hd].float().cpu().view(H, hd)
+        ref = _ref_attention(q, ks[t].to(dt).float(), vs[t].to(dt).float(), n - 1, 1 / math.sqrt(hd), window)
+        _close(out[t].view(H, hd), ref, "bfloat16", f"decode attention row {t} (len {n})", scale=float(vs[t].abs().max()))
+
+
+@pytest.mark.parametrize("splits", [1, 4, 32])
+def test_attention_decode_finds_one_far_key_among_thousands(ops, splits):
+    torch.manual_seed(14)
+    dt = torch.bfloat16
+    H, KV, hd, n = 8, 2, 128, 3000
+    cache = Paged(2, 3072, KV, hd, dt, seed=5)
+    k = torch.randn(n, KV, hd) * 0.1
+    v = torch.randn(n, KV, hd)
+    q = torch.randn(H, hd) * 0.1
+    q[:, 9] = 40.0
+    for far in (0, 63, 64, 1999, 2999):
+        kk = k.clone()
+        kk[far] = 0
+        kk[far, :, 9] = 40.0
+        _fill_cache(cache, 1, kk, v)
+        qbuf = q.view(1, H * hd).to(dt).to(DEV)
+        out = torch.empty(1, H * hd, device=DEV, dtype=dt)
+        pos = torch.tensor([n - 1], dtype=torch.int32, device=DEV)
+        tslot = torch.tensor([1], dtype=torch.int32, device=DEV)
+        ops.attention_decode(qbuf, H * hd, out, cache.k, cache.v, cache.table, pos, tslot, 1, H, KV, hd, 1 / math.sqrt(hd), 0, splits)
+        want = v[far].to(dt).float().repeat_interleave(H // KV, dim=0)
+        _close(out.view(H, hd), want, "bfloat16", f"far key at {far}, {splits} splits")
