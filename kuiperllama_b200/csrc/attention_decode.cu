@@ -261,3 +261,48 @@ KL_API int kl_attention_decode(const void* q, int q_stride, void* out, const voi
     }
 #undef KL_DA
 }
+
+// ------------------------------------------------------------------------------------------
+// The variant that allocates nothing (see attention_decode_noalloc.h for who needs it and why).
+#include "attention_decode_noalloc.h"
+#include <stdio.h>
+
+// Scratch for the splits' partial results.  In host code this name is only a stand-in for the
+// device symbol, not a device address: the address is asked for once per device below.
+static __device__ __align__(256) float g_decode_noalloc_scratch[KL_DECODE_NOALLOC_FLOATS];
+
+static constexpr int KL_MAX_DEVICES = 64;
+static float* g_decode_noalloc_ptr[KL_MAX_DEVICES] = {nullptr};
+
+KL_API int kl_attention_decode_noalloc(const void* q, int q_stride, void* out, const void* k_cache,
+                                       const void* v_cache, const int* block_table, int blocks_per_seq,
+                                       const int* positions, const int* token_slot, int rows, int H, int KV, int hd,
+                                       float scale, int window, int splits, cudaStream_t stream) {
+    if (rows <= 0) return KL_OK;
+    if (splits < 1 || H <= 0 || hd <= 0) return KL_ERR_BAD_SIZE;
+    const long long need = (long long)rows * H * splits * (hd + 2);
+    if (need > (long long)KL_DECODE_NOALLOC_FLOATS) {
+        fprintf(stderr, "[kuiperllama_b200] kl_attention_decode_noalloc: rows %d x heads %d x splits %d x (head_dim %d + 2) = "
+                        "%lld float32 values of scratch exceed the built-in %d; use fewer splits or kl_attention_decode\n",
+                rows, H, splits, hd, need, KL_DECODE_NOALLOC_FLOATS);
+        return KL_ERR_BAD_SIZE;
+    }
+    int dev = -1;
+    KL_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= KL_MAX_DEVICES) return KL_ERR_SETUP;
+    if (g_decode_noalloc_ptr[dev] == nullptr) {
+        // First call on this device (it is the current one): the array's address there.
+        float* p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress((void**)&p, g_decode_noalloc_scratch);
+        if (e != cudaSuccess || p == nullptr) {
+            fprintf(stderr, "[kuiperllama_b200] kl_attention_decode_noalloc: cudaGetSymbolAddress failed: %s\n",
+                    cudaGetErrorString(e));
+            return e != cudaSuccess ? (int)e : KL_ERR_SETUP;
+        }
+        g_decode_noalloc_ptr[dev] = p;
+    }
+    float* partial_o = g_decode_noalloc_ptr[dev];                       // [rows, H, splits, hd]
+    float* partial_ml = partial_o + (size_t)rows * H * splits * hd;     // [rows, H, splits, 2]
+    return kl_attention_decode(q, q_stride, out, k_cache, v_cache, block_table, blocks_per_seq, positions, token_slot,
+                               partial_o, partial_ml, rows, H, KV, hd, scale, window, splits, stream);
+}

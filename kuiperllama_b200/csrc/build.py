@@ -33,7 +33,7 @@ SOURCES: Dict[str, str] = {
     "gemm_tcgen05": "gemm_tcgen05.cu",
     "sampling": "sampling.cu",
 }
-HEADERS: List[str] = ["common.cuh"]
+HEADERS: List[str] = ["common.cuh", "attention_decode_noalloc.h"]
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-shared", "--expt-relaxed-constexpr"]
