@@ -36,7 +36,7 @@ SOURCES: Dict[str, str] = {
 HEADERS: List[str] = ["common.cuh", "attention_decode_noalloc.h"]
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-              "-Xcompiler", "-fPIC", "-shared", "--expt-relaxed-constexpr"]
+              "-Xcompiler", "-fPIC", "-shared", "--expt-relaxed-constexpr", "--extended-lambda"]
 
 
 class ExtensionError(RuntimeError):

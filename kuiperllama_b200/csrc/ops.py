@@ -107,13 +107,20 @@ def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, error_f
                                        _ptr(out), _ptr(error_flag), _stream()), "embedding")
 
 
+def _partials(delta: Optional[torch.Tensor]) -> bool:
+    """A delta given as float32 partial sums [S, rows, width] (the pieces of a product whose K
+    range was cut), to be added in ascending order by the kernel that consumes it."""
+    return delta is not None and delta.dim() == 3
+
+
 def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, out: torch.Tensor,
                 eps: float, rows: Optional[torch.Tensor] = None) -> None:
     """x = residual (+ delta); out = weight * x * rsqrt(mean(x^2) + eps).
 
-    Without ``rows`` every row is processed and, when ``delta`` is given, the sum is written
-    back to ``residual``.  With ``rows`` (int32 indices) only those rows are read, into
-    out[0..len(rows)), and ``residual`` is left as it is."""
+    ``delta`` is [rows, hidden] in the output's dtype, or float32 partial sums
+    [S, rows, hidden].  Without ``rows`` every row is processed and, when ``delta`` is given,
+    the sum is written back to ``residual``.  With ``rows`` (int32 indices) only those rows
+    are read, into out[0..len(rows)), and ``residual`` is left as it is."""
     _cuda(residual, delta, weight, out, rows)
     _i32(rows, "rows")
     hidden = residual.shape[-1]
@@ -121,11 +128,17 @@ def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: t
     _need(residual.dtype == torch.float32 and residual.is_contiguous(), "add_rmsnorm: the residual stream is float32")
     _need(weight.dtype == torch.float32 and weight.numel() == hidden, "add_rmsnorm: weight must be float32 [hidden]")
     _need(out.is_contiguous() and out.shape[-1] == hidden and out.shape[0] >= n, "add_rmsnorm: output shape")
-    if delta is not None:
+    plain, parts, n_parts, stride = delta, None, 0, 0
+    if _partials(delta):
+        _need(delta.dtype == torch.float32 and delta.is_contiguous() and tuple(delta.shape[1:]) == tuple(residual.shape),
+              "add_rmsnorm: partial sums must be float32 [S, rows, hidden]")
+        plain, parts, n_parts, stride = None, delta, delta.shape[0], delta.shape[1] * delta.shape[2]
+    elif delta is not None:
         _need(delta.dtype == out.dtype and delta.is_contiguous() and delta.shape == residual.shape,
               "add_rmsnorm: delta must match the residual's shape and the output's dtype")
-    _check(lib("rowwise").kl_add_rmsnorm(_ptr(residual), _ptr(delta), _ptr(weight), _ptr(out), _ptr(rows), n, hidden,
-                                         ctypes.c_float(eps), dtype_code(out.dtype), _stream()), "add_rmsnorm")
+    _check(lib("rowwise").kl_add_rmsnorm(_ptr(residual), _ptr(plain), _ptr(parts), n_parts, ctypes.c_longlong(stride),
+                                         _ptr(weight), _ptr(out), _ptr(rows), n, hidden, ctypes.c_float(eps),
+                                         dtype_code(out.dtype), _stream()), "add_rmsnorm")
 
 
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
@@ -142,11 +155,19 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
 
 def rope_kv_write(qkv: torch.Tensor, inv_freq: Optional[torch.Tensor], rotary_dim: int, positions: torch.Tensor,
                   token_slot: torch.Tensor, block_table: torch.Tensor, k_cache: Optional[torch.Tensor],
-                  v_cache: Optional[torch.Tensor], num_heads: int, num_kv_heads: int, head_dim: int) -> None:
+                  v_cache: Optional[torch.Tensor], num_heads: int, num_kv_heads: int, head_dim: int,
+                  partials: Optional[torch.Tensor] = None) -> None:
     """Rotate the query heads of ``qkv`` [tokens, (H + 2 KV) * hd] in place; rotate the key
     heads and store them, and the value heads, into the paged cache
-    [pages, KV, PAGE, hd] (skipped when both caches are None)."""
-    _cuda(qkv, inv_freq, positions, token_slot, block_table, k_cache, v_cache)
+    [pages, KV, PAGE, hd] (skipped when both caches are None).  With ``partials`` (float32
+    [S, tokens, width]) the projections are the sum of those pieces and ``qkv`` only receives
+    the rotated queries."""
+    _cuda(qkv, inv_freq, positions, token_slot, block_table, k_cache, v_cache, partials)
+    n_parts, stride = 0, 0
+    if partials is not None:
+        _need(partials.dtype == torch.float32 and partials.is_contiguous() and tuple(partials.shape[1:]) == tuple(qkv.shape),
+              "rope_kv_write: partial sums must be float32 [S, tokens, width]")
+        n_parts, stride = partials.shape[0], partials.shape[1] * partials.shape[2]
     _i32(positions, "positions"); _i32(token_slot, "token_slot"); _i32(block_table, "block_table")
     n = qkv.shape[0]
     _need(qkv.is_contiguous() and qkv.shape[1] == (num_heads + 2 * num_kv_heads) * head_dim, "rope_kv_write: qkv shape")
@@ -160,7 +181,8 @@ def rope_kv_write(qkv: torch.Tensor, inv_freq: Optional[torch.Tensor], rotary_di
     if rotary_dim:
         _need(inv_freq is not None and inv_freq.dtype == torch.float32 and inv_freq.numel() == rotary_dim // 2,
               "rope_kv_write: inv_freq must be float32 [rotary_dim / 2]")
-    _check(lib("rope_kv").kl_rope_kv_write(_ptr(qkv), _ptr(inv_freq), rotary_dim, _ptr(positions), _ptr(token_slot),
+    _check(lib("rope_kv").kl_rope_kv_write(_ptr(qkv), _ptr(partials), n_parts, ctypes.c_longlong(stride),
+                                           _ptr(inv_freq), rotary_dim, _ptr(positions), _ptr(token_slot),
                                            _ptr(block_table), block_table.shape[1], _ptr(k_cache), _ptr(v_cache), n,
                                            num_heads, num_kv_heads, head_dim, int(write), dtype_code(qkv.dtype),
                                            _stream()), "rope_kv_write")
@@ -207,8 +229,16 @@ def argmax_rows(logits: torch.Tensor, out: torch.Tensor) -> None:
     _i32(out, "out")
     rows, vocab = logits.shape
     _need(logits.dtype == torch.float32 and logits.stride(1) == 1 and out.numel() >= rows, "argmax: layout")
-    _check(lib("sampling").kl_argmax_rows(_ptr(logits), ctypes.c_longlong(logits.stride(0)), rows, vocab, _ptr(out),
-                                          _stream()), "argmax_rows")
+    L = lib("sampling")
+    sv = si = None
+    launches = 1
+    if vocab >= 16384:                                              # wide rows: many CTAs per row, then one pick
+        chunks = L.kl_argmax_chunks(vocab)
+        sv = torch.empty((rows, chunks), dtype=torch.float32, device=logits.device)
+        si = torch.empty((rows, chunks), dtype=torch.int32, device=logits.device)
+        launches = 2
+    _check(L.kl_argmax_rows(_ptr(logits), ctypes.c_longlong(logits.stride(0)), rows, vocab, _ptr(out), _ptr(sv), _ptr(si),
+                            _stream()), "argmax_rows", launches)
 
 
 def sample_rows(logits: torch.Tensor, temperature: float, top_k: int, seed: int, request_ids: torch.Tensor,
@@ -280,6 +310,26 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
                                                ctypes.c_longlong(w.stride(0)), _ptr(out), ctypes.c_longlong(out.stride(0)),
                                                M, N, K, int(out.dtype == torch.float32), _ptr(status_word(a.device)),
                                                _stream()), "gemm_tcgen05")
+
+
+def gemm_skinny_partials(a: torch.Tensor, w: torch.Tensor, splits: Optional[int] = None) -> Optional[torch.Tensor]:
+    """The pieces of a @ w^T for M <= 64 tokens as float32 [S, M, N], for a consumer that adds
+    them itself (the norm after a projection, the rotary kernel after q/k/v); None when the
+    product is not cut (S == 1) or the operands do not fit the tensor-core kernel."""
+    (M, K), (N, K2) = a.shape, w.shape
+    if M > 64 or a.dtype != torch.bfloat16 or K != K2:
+        return None
+    probe = torch.empty((0, N), dtype=torch.float32, device=a.device)
+    if not _tc_ok(a, w, probe):
+        return None
+    splits = skinny_splits(N, K) if splits is None else splits
+    if splits <= 1:
+        return None
+    partial = torch.empty((splits, M, N), dtype=torch.float32, device=a.device)
+    _check(lib("gemm_tcgen05").kl_gemm_tcgen05_skinny(
+        _ptr(a), ctypes.c_longlong(a.stride(0)), _ptr(w), ctypes.c_longlong(w.stride(0)), _ptr(partial),
+        ctypes.c_longlong(N), M, N, K, splits, 1, _ptr(status_word(a.device)), _stream()), "gemm_skinny")
+    return partial
 
 
 def gemm_skinny(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, splits: Optional[int] = None) -> None:

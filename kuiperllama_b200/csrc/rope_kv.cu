@@ -13,8 +13,12 @@
 namespace kl {
 
 // qkv: [tokens, (H + 2 KV) * hd], query heads first, then key heads, then value heads.
+// With n_partials > 0 the projections arrive as float32 partial sums
+// [n_partials][tokens][(H + 2 KV) * hd] of a product whose K range was cut: they are added in
+// ascending order here, rotated in float32, and qkv only receives the rotated queries.
 template <typename T>
-__global__ void rope_kv_write_kernel(T* __restrict__ qkv, const float* __restrict__ inv_freq, int rot,
+__global__ void rope_kv_write_kernel(T* __restrict__ qkv, const float* __restrict__ partials, int n_partials,
+                                     size_t partial_stride, const float* __restrict__ inv_freq, int rot,
                                      const int* __restrict__ positions, const int* __restrict__ token_slot,
                                      const int* __restrict__ block_table, int blocks_per_seq,
                                      T* __restrict__ k_cache, T* __restrict__ v_cache,
@@ -23,9 +27,27 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const float* __restric
     const int slot = token_slot[t];
     if (slot < 0) return;                                   // a padding row
     const int pos = positions[t];
-    T* row = qkv + (size_t)t * (H + 2 * KV) * hd;
+    const int width = (H + 2 * KV) * hd;
+    T* row = qkv + (size_t)t * width;
+    const float* prow = n_partials > 0 ? partials + (size_t)t * width : nullptr;
+    auto value = [&](int idx) {                             // element idx of this token's q|k|v row, in float32
+        if (prow == nullptr) return to_f32(row[idx]);
+        float a = 0.f;
+        for (int z = 0; z < n_partials; ++z) a += prow[(size_t)z * partial_stride + idx];
+        return a;
+    };
     const int half = hd / 2;                                // work items per head: hd/2 pairs of lanes
     const int rhalf = rot / 2;
+    if (prow != nullptr && rot != hd) {
+        // partial or no rotation: first put the summed row down, then go on as without partials
+        for (int idx = threadIdx.x; idx < width; idx += blockDim.x) {
+            float a = 0.f;
+            for (int z = 0; z < n_partials; ++z) a += prow[(size_t)z * partial_stride + idx];
+            row[idx] = from_f32<T>(a);
+        }
+        prow = nullptr;
+        __syncthreads();
+    }
     // queries and keys: (head, j) with j in [0, hd/2): element j and element j + hd/2 are
     // handled together so that each thread owns what it reads and writes.
     const int n_qk = (H + KV) * half;
@@ -35,7 +57,8 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const float* __restric
         T* h = row + (size_t)head * hd;
         // the two elements this thread owns
         const int e0 = j, e1 = j + half;
-        float v0 = to_f32(h[e0]), v1 = to_f32(h[e1]);
+        if (rot != hd) break;                               // handled below
+        float v0 = value(head * hd + e0), v1 = value(head * hd + e1);
         if (rot == hd) {
             float s, c;
             sincosf((float)pos * inv_freq[j], &s, &c);
@@ -78,11 +101,10 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const float* __restric
         }
     }
     if (write_kv) {
-        const T* vsrc = row + (size_t)(H + KV) * hd;
         for (int idx = threadIdx.x; idx < KV * hd; idx += blockDim.x) {
             const int g = idx / hd, e = idx - g * hd;
             T* dst = v_cache + cache_row_offset(block_table, blocks_per_seq, slot, pos, g, KV, hd);
-            dst[e] = vsrc[idx];
+            dst[e] = from_f32<T>(value((H + KV) * hd + idx));
         }
     }
 }
@@ -91,20 +113,24 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const float* __restric
 
 using namespace kl;
 
-KL_API int kl_rope_kv_write(void* qkv, const float* inv_freq, int rotary_dim, const int* positions,
+KL_API int kl_rope_kv_write(void* qkv, const float* partials, int n_partials, long long partial_stride,
+                            const float* inv_freq, int rotary_dim, const int* positions,
                             const int* token_slot, const int* block_table, int blocks_per_seq, void* k_cache,
                             void* v_cache, int n_tokens, int H, int KV, int hd, int write_kv, int dtype,
                             cudaStream_t stream) {
     if (n_tokens <= 0) return KL_OK;
     if (hd % 2 || rotary_dim % 2 || rotary_dim > hd || rotary_dim < 0) return KL_ERR_BAD_SIZE;
     if (rotary_dim > 0 && inv_freq == nullptr) return KL_ERR_BAD_SIZE;
+    if (n_partials < 0 || (n_partials > 0 && partials == nullptr)) return KL_ERR_BAD_SIZE;
     const int work = (H + KV) * hd / 2;
-    const int threads = work >= 1024 ? 256 : (work >= 256 ? 128 : 64);
+    const int threads = work >= 2048 ? 512 : (work >= 1024 ? 256 : (work >= 256 ? 128 : 64));
     if (dtype == KL_F32)
-        rope_kv_write_kernel<float><<<n_tokens, threads, 0, stream>>>((float*)qkv, inv_freq, rotary_dim, positions,
+        rope_kv_write_kernel<float><<<n_tokens, threads, 0, stream>>>((float*)qkv, partials, n_partials,
+            (size_t)partial_stride, inv_freq, rotary_dim, positions,
             token_slot, block_table, blocks_per_seq, (float*)k_cache, (float*)v_cache, H, KV, hd, write_kv);
     else if (dtype == KL_BF16)
-        rope_kv_write_kernel<bf16><<<n_tokens, threads, 0, stream>>>((bf16*)qkv, inv_freq, rotary_dim, positions,
+        rope_kv_write_kernel<bf16><<<n_tokens, threads, 0, stream>>>((bf16*)qkv, partials, n_partials,
+            (size_t)partial_stride, inv_freq, rotary_dim, positions,
             token_slot, block_table, blocks_per_seq, (bf16*)k_cache, (bf16*)v_cache, H, KV, hd, write_kv);
     else
         return KL_ERR_BAD_DTYPE;

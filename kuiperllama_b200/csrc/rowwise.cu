@@ -29,59 +29,115 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restric
 }
 
 // One CTA per output row r.  Source row s = rows ? rows[r] : r.
-//   x = residual[s] (+ delta[s] if delta);  if (!rows && delta) residual[s] = x;
+//   x = residual[s] + delta[s] (+ partial[0][s] + partial[1][s] + ... in ascending order)
+//   if (!rows && something was added) residual[s] = x
 //   out[r] = weight * x * rsqrt(mean(x^2) + eps)
-// With `rows` the residual is not written back: it is the read of a few rows before the
-// classifier.  The row is kept in registers between the two passes (hidden <= 256 * 32),
-// else it is read twice.
-template <typename T, int THREADS, int PER_THREAD>
-__global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __restrict__ delta,
-                                   const float* __restrict__ weight, T* __restrict__ out,
-                                   const int* __restrict__ rows, int hidden, float eps) {
+// `delta` is in the compute dtype; `partials` are float32 partial sums [n_partials][rows][hidden]
+// of a product whose K range was cut (their sum is the delta).  With `rows` the residual is
+// not written back: it is the read of a few rows before the classifier.  Rows are processed
+// four floats at a time when hidden is a multiple of 4; a row that fits THREADS * 4 * VPT
+// floats stays in registers between the two passes, else it is recomputed.
+template <typename T> struct Delta4;
+template <> struct Delta4<float> {
+    static __device__ __forceinline__ float4 load(const float* p) { return *reinterpret_cast<const float4*>(p); }
+    static __device__ __forceinline__ void store(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+};
+template <> struct Delta4<bf16> {
+    static __device__ __forceinline__ float4 load(const bf16* p) {
+        const uint2 raw = *reinterpret_cast<const uint2*>(p);
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+        return make_float4(a.x, a.y, b.x, b.y);
+    }
+    static __device__ __forceinline__ void store(bf16* p, float4 v) {
+        __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+        uint2 raw;
+        raw.x = *reinterpret_cast<uint32_t*>(&a);
+        raw.y = *reinterpret_cast<uint32_t*>(&b);
+        *reinterpret_cast<uint2*>(p) = raw;
+    }
+};
+
+template <typename T, int THREADS, int VPT>
+__global__ void __launch_bounds__(THREADS)
+add_rmsnorm_kernel(float* __restrict__ residual, const T* __restrict__ delta, const float* __restrict__ partials,
+                   int n_partials, size_t partial_stride, const float* __restrict__ weight, T* __restrict__ out,
+                   const int* __restrict__ rows, int hidden, float eps) {
     __shared__ float scratch[33];
     const int r = blockIdx.x;
     const int s = rows ? rows[r] : r;
     float* x = residual + (size_t)s * hidden;
     const T* d = delta ? delta + (size_t)s * hidden : nullptr;
+    const float* p = n_partials > 0 ? partials + (size_t)s * hidden : nullptr;
     T* o = out + (size_t)r * hidden;
-    const bool write_back = (rows == nullptr) && (delta != nullptr);
-    float v[PER_THREAD];
+    const bool adds = d != nullptr || p != nullptr;
+    const bool write_back = rows == nullptr && adds;
     float ss = 0.f;
-    const bool in_regs = hidden <= THREADS * PER_THREAD;
-    if (in_regs) {
-#pragma unroll
-        for (int j = 0; j < PER_THREAD; ++j) {
-            const int i = threadIdx.x + j * THREADS;
-            float a = 0.f;
-            if (i < hidden) {
-                a = x[i];
-                if (d) a += to_f32(d[i]);
-                if (write_back) x[i] = a;
+    if ((hidden & 3) == 0) {
+        const int n4 = hidden >> 2;
+        auto value = [&](int i4) {
+            float4 a = *reinterpret_cast<const float4*>(x + 4 * i4);
+            if (d) { const float4 b = Delta4<T>::load(d + 4 * i4); a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w; }
+            for (int z = 0; z < n_partials; ++z) {
+                const float4 b = *reinterpret_cast<const float4*>(p + (size_t)z * partial_stride + 4 * i4);
+                a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
             }
-            v[j] = a;
-            ss += a * a;
+            return a;
+        };
+        float4 v[VPT];
+        const bool in_regs = n4 <= THREADS * VPT;
+        if (in_regs) {
+#pragma unroll
+            for (int j = 0; j < VPT; ++j) {
+                const int i4 = threadIdx.x + j * THREADS;
+                float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (i4 < n4) {
+                    a = value(i4);
+                    if (write_back) *reinterpret_cast<float4*>(x + 4 * i4) = a;
+                }
+                v[j] = a;
+                ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+            }
+        } else {
+            for (int i4 = threadIdx.x; i4 < n4; i4 += THREADS) {
+                const float4 a = value(i4);
+                ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+            }
+        }
+        ss = block_sum(ss, scratch);
+        const float inv = rsqrtf(ss / (float)hidden + eps);
+        if (in_regs) {
+#pragma unroll
+            for (int j = 0; j < VPT; ++j) {
+                const int i4 = threadIdx.x + j * THREADS;
+                if (i4 < n4) {
+                    const float4 w = *reinterpret_cast<const float4*>(weight + 4 * i4);
+                    const float4 a = v[j];
+                    Delta4<T>::store(o + 4 * i4, make_float4(w.x * (a.x * inv), w.y * (a.y * inv), w.z * (a.z * inv), w.w * (a.w * inv)));
+                }
+            }
+        } else {
+            for (int i4 = threadIdx.x; i4 < n4; i4 += THREADS) {
+                const float4 a = value(i4);                      // the residual is still unchanged: recompute, then write
+                const float4 w = *reinterpret_cast<const float4*>(weight + 4 * i4);
+                Delta4<T>::store(o + 4 * i4, make_float4(w.x * (a.x * inv), w.y * (a.y * inv), w.z * (a.z * inv), w.w * (a.w * inv)));
+                if (write_back) *reinterpret_cast<float4*>(x + 4 * i4) = a;
+            }
         }
     } else {
-        for (int i = threadIdx.x; i < hidden; i += THREADS) {
+        auto value = [&](int i) {
             float a = x[i];
             if (d) a += to_f32(d[i]);
-            if (write_back) x[i] = a;
-            ss += a * a;
-        }
-    }
-    ss = block_sum(ss, scratch);
-    const float inv = rsqrtf(ss / (float)hidden + eps);
-    if (in_regs) {
-#pragma unroll
-        for (int j = 0; j < PER_THREAD; ++j) {
-            const int i = threadIdx.x + j * THREADS;
-            if (i < hidden) o[i] = from_f32<T>(weight[i] * (v[j] * inv));
-        }
-    } else {
+            for (int z = 0; z < n_partials; ++z) a += p[(size_t)z * partial_stride + i];
+            return a;
+        };
+        for (int i = threadIdx.x; i < hidden; i += THREADS) { const float a = value(i); ss += a * a; }
+        ss = block_sum(ss, scratch);
+        const float inv = rsqrtf(ss / (float)hidden + eps);
         for (int i = threadIdx.x; i < hidden; i += THREADS) {
-            float a = x[i];
-            if (d && !write_back) a += to_f32(d[i]);
+            const float a = value(i);
             o[i] = from_f32<T>(weight[i] * (a * inv));
+            if (write_back) x[i] = a;
         }
     }
 }
@@ -117,18 +173,22 @@ KL_API int kl_embedding(const int* ids, int n_tokens, const void* table, int tab
     return KL_OK;
 }
 
-KL_API int kl_add_rmsnorm(float* residual, const void* delta, const float* weight, void* out, const int* rows,
-                          int n_rows, int hidden, float eps, int dtype, cudaStream_t stream) {
+// delta: compute dtype [rows, hidden] or null; partials: float32 [n_partials, rows_total, hidden]
+// or null (partial_stride = rows_total * hidden elements).
+KL_API int kl_add_rmsnorm(float* residual, const void* delta, const float* partials, int n_partials,
+                          long long partial_stride, const float* weight, void* out, const int* rows, int n_rows,
+                          int hidden, float eps, int dtype, cudaStream_t stream) {
     if (n_rows <= 0) return KL_OK;
-    constexpr int THREADS = 256, PER = 32;
-    if (dtype == KL_F32)
-        add_rmsnorm_kernel<float, THREADS, PER><<<n_rows, THREADS, 0, stream>>>(residual, (const float*)delta, weight,
-                                                                               (float*)out, rows, hidden, eps);
-    else if (dtype == KL_BF16)
-        add_rmsnorm_kernel<bf16, THREADS, PER><<<n_rows, THREADS, 0, stream>>>(residual, (const bf16*)delta, weight,
-                                                                              (bf16*)out, rows, hidden, eps);
-    else
-        return KL_ERR_BAD_DTYPE;
+    if (n_partials < 0 || (n_partials > 0 && partials == nullptr)) return KL_ERR_BAD_SIZE;
+    // few rows: more threads per row, so that a step of a handful of tokens is not one slow CTA each
+    const bool wide = n_rows <= 256 && hidden >= 2048;
+#define KL_NORM(T, THREADS)                                                                                          \
+    add_rmsnorm_kernel<T, THREADS, 8><<<n_rows, THREADS, 0, stream>>>(residual, (const T*)delta, partials, n_partials, \
+        (size_t)partial_stride, weight, (T*)out, rows, hidden, eps)
+    if (dtype == KL_F32) { if (wide) KL_NORM(float, 1024); else KL_NORM(float, 256); }
+    else if (dtype == KL_BF16) { if (wide) KL_NORM(bf16, 1024); else KL_NORM(bf16, 256); }
+    else return KL_ERR_BAD_DTYPE;
+#undef KL_NORM
     KL_LAUNCH_CHECK();
     return KL_OK;
 }

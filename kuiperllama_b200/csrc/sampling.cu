@@ -53,6 +53,60 @@ argmax_rows_kernel(const float* __restrict__ logits, size_t row_stride, int voca
     }
 }
 
+// Two-stage argmax for wide rows: grid (chunks, rows) writes each chunk's best (value, index),
+// then one warp per row picks among the chunks.  Ties go to the lower index in both stages.
+constexpr int ARGMAX_CHUNK = 4096;
+
+__global__ void __launch_bounds__(256)
+argmax_chunks_kernel(const float* __restrict__ logits, size_t row_stride, int vocab, float* __restrict__ best_v,
+                     int* __restrict__ best_i) {
+    __shared__ float sv[8];
+    __shared__ int si[8];
+    const int row = blockIdx.y, chunk = blockIdx.x;
+    const float* x = logits + (size_t)row * row_stride;
+    const int begin = chunk * ARGMAX_CHUNK, end = min(begin + ARGMAX_CHUNK, vocab);
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
+        const float v = x[i];
+        if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    if (lane == 0) { sv[warp] = best; si[warp] = bi; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < 8; ++w)
+            if (sv[w] > best || (sv[w] == best && si[w] < bi)) { best = sv[w]; bi = si[w]; }
+        best_v[(size_t)row * gridDim.x + chunk] = best;
+        best_i[(size_t)row * gridDim.x + chunk] = bi;
+    }
+}
+
+__global__ void argmax_pick_kernel(const float* __restrict__ best_v, const int* __restrict__ best_i, int chunks,
+                                   int* __restrict__ out) {
+    const int row = blockIdx.x;
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int c = threadIdx.x; c < chunks; c += 32) {
+        const float v = best_v[(size_t)row * chunks + c];
+        const int i = best_i[(size_t)row * chunks + c];
+        if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    if (threadIdx.x == 0) out[row] = bi == 0x7fffffff ? 0 : bi;
+}
+
 // The uniform draw in [0, 1) of (seed, request, step): a 64-bit mix, top 24 bits.
 __device__ __forceinline__ float uniform_from_counter(unsigned long long seed, unsigned long long request,
                                                       unsigned long long step) {
@@ -159,11 +213,24 @@ sample_rows_kernel(const float* __restrict__ logits, size_t row_stride, int voca
 
 using namespace kl;
 
-KL_API int kl_argmax_rows(const float* logits, long long row_stride, int rows, int vocab, int* out,
-                          cudaStream_t stream) {
+// Chunks a row is cut into by the two-stage argmax (the caller sizes scratch with it).
+KL_API int kl_argmax_chunks(int vocab) { return (vocab + ARGMAX_CHUNK - 1) / ARGMAX_CHUNK; }
+
+// scratch_v / scratch_i: [rows, kl_argmax_chunks(vocab)] float32 / int32, or null for the
+// single-stage kernel (one CTA per row).
+KL_API int kl_argmax_rows(const float* logits, long long row_stride, int rows, int vocab, int* out, float* scratch_v,
+                          int* scratch_i, cudaStream_t stream) {
     if (rows <= 0) return KL_OK;
     if (vocab <= 0) return KL_ERR_BAD_SIZE;
-    argmax_rows_kernel<<<rows, SAMPLE_THREADS, 0, stream>>>(logits, (size_t)row_stride, vocab, out);
+    if (scratch_v == nullptr || scratch_i == nullptr || rows > 65535) {
+        argmax_rows_kernel<<<rows, SAMPLE_THREADS, 0, stream>>>(logits, (size_t)row_stride, vocab, out);
+        KL_LAUNCH_CHECK();
+        return KL_OK;
+    }
+    const int chunks = (vocab + ARGMAX_CHUNK - 1) / ARGMAX_CHUNK;
+    argmax_chunks_kernel<<<dim3(chunks, rows), 256, 0, stream>>>(logits, (size_t)row_stride, vocab, scratch_v, scratch_i);
+    KL_LAUNCH_CHECK();
+    argmax_pick_kernel<<<rows, 32, 0, stream>>>(scratch_v, scratch_i, chunks, out);
     KL_LAUNCH_CHECK();
     return KL_OK;
 }

@@ -59,11 +59,14 @@ class AttentionMixer(Mixer):
 
     def forward(self, x: torch.Tensor, step: StepContext, cache: CacheView) -> torch.Tensor:
         n = step.n_tokens
-        qkv = self.qkv.forward(x)
+        qkv = self.qkv.forward(x, allow_partials=True)
+        parts = None
+        if qkv.dim() == 3:                                         # pieces of the product: the rotary kernel adds them
+            parts, qkv = qkv, torch.empty(qkv.shape[1:], dtype=self.runtime.dtype, device=x.device)
         ops.rope_kv_write(qkv, self.inv_freq, self.rotary_dim, step.positions, step.token_slot, cache.block_table,
                           cache.k if cache.writable else None, cache.v if cache.writable else None,
-                          self.H, self.KV, self.hd)
+                          self.H, self.KV, self.hd, partials=parts)
         attn = torch.empty((n, self.H * self.hd), dtype=self.runtime.dtype, device=x.device)
         ops.attention(qkv, qkv.shape[1], attn, cache.k, cache.v, cache.block_table, step, self.H, self.KV, self.hd,
                       self.scale, int(self.window or 0))
-        return self.o.forward(attn)
+        return self.o.forward(attn, allow_partials=True)

@@ -69,9 +69,10 @@ class Part:
 
 
 class Norm(Part):
-    """``forward(residual, delta, out_rows)``: adds ``delta`` (may be None) to the float32
-    residual stream in place and returns the normalised rows in the compute dtype.  With
-    ``rows`` only those rows are produced and the residual is left unchanged."""
+    """``forward(residual, delta, n_rows, rows)``: adds ``delta`` (None, [n, hidden] in the
+    compute dtype, or float32 partial sums [S, n, hidden]) to the float32 residual stream in
+    place and returns the normalised rows in the compute dtype.  With ``rows`` only those rows
+    are produced and the residual is left unchanged."""
 
     def forward(self, residual: torch.Tensor, delta: Optional[torch.Tensor], n_rows: int,
                 rows: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -94,7 +95,9 @@ class Mixer(Part):
     """Mixes information between the tokens of a sequence.  ``kv_request`` / ``state_request``
     say what the cache must hold for one execution; ``forward`` gets the normalised rows
     [n_tokens, hidden], the step and its view of the cache, and returns [n_tokens, hidden]
-    in the compute dtype (the block adds it to the residual stream)."""
+    in the compute dtype (the block adds it to the residual stream).  It may instead return
+    float32 partial sums [S, n_tokens, hidden] whose sum over S is that result; the norm
+    that follows adds them in ascending order."""
 
     def __init__(self, spec, prefix, tensors, runtime, position: Optional[PositionEncoding] = None):
         super().__init__(spec, prefix, tensors, runtime)
@@ -111,7 +114,8 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
-    """``forward(x, step)``: [n_tokens, hidden] -> [n_tokens, hidden], token by token."""
+    """``forward(x, step)``: [n_tokens, hidden] -> [n_tokens, hidden], token by token (or
+    float32 partial sums [S, n_tokens, hidden], as a mixer may)."""
 
     def forward(self, x: torch.Tensor, step: StepContext) -> torch.Tensor:
         raise NotImplementedError

@@ -24,8 +24,15 @@ class Linear:
         self.runtime = runtime
 
     def forward(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
-                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                out: Optional[torch.Tensor] = None, allow_partials: bool = False) -> torch.Tensor:
+        """[m, in] -> [m, out].  With ``allow_partials`` the result may instead be float32
+        partial sums [S, m, out] (a product of few tokens whose K range was cut over CTAs);
+        the norm and the rotary kernel add such pieces themselves, which saves a pass."""
         m = x.shape[0]
+        if allow_partials and out is None:
+            parts = ops.gemm_skinny_partials(x, self.weight)
+            if parts is not None:
+                return parts
         if out is None:
             out = torch.empty((m, self.out_features), dtype=out_dtype or self.runtime.dtype, device=x.device)
         ops.matmul(x, self.weight, out)

@@ -38,4 +38,4 @@ class SwiGLUFeedForward(FeedForward):
         gu = self.gate_up.forward(x)
         act = torch.empty((x.shape[0], self.inter), dtype=self.runtime.dtype, device=x.device)
         ops.swiglu(gu, act)
-        return self.down.forward(act)
+        return self.down.forward(act, allow_partials=True)

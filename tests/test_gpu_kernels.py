@@ -76,6 +76,13 @@ def test_add_rmsnorm(ops, dtype, hidden):
     assert torch.equal(resid, before)
     x2 = (before + delta.float())[rows.long()]
     _close(out2, plain_llama.rmsnorm(x2.cpu(), w.cpu(), eps), dtype, "gathered rows")
+    # a delta given as float32 partial sums [S, rows, hidden], added in ascending order
+    parts = torch.randn(3, T, hidden, device=DEV)
+    before = resid.clone()
+    ops.add_rmsnorm(resid, parts, w, out, eps)
+    x3 = ((before + parts[0]) + parts[1]) + parts[2]
+    assert torch.equal(resid, x3), "partial sums are not added in ascending order in float32"
+    _close(out, plain_llama.rmsnorm(x3.cpu(), w.cpu(), eps), dtype, "partial sums + rmsnorm")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -191,6 +198,24 @@ def test_rope_kv_write(ops, dtype, H, KV, hd, rot):
         o += n
     assert torch.equal(cache.k[~written], before_k[~written]) and torch.equal(cache.v[~written], before_v[~written]), \
         "something outside the new tokens' rows was written"
+    # the same projections given as three float32 pieces: same queries and cache rows
+    cache2 = Paged(4, 256, KV, hd, dt, seed=1)
+    full = qkv.float()
+    pieces = torch.randn(3, *full.shape, device=DEV)
+    pieces[2] = full - (pieces[0] + pieces[1])
+    exact = ((pieces[0] + pieces[1]) + pieces[2])
+    y = torch.zeros_like(qkv)
+    ops.rope_kv_write(y, inv, rot, pos, tslot, cache2.table, cache2.k, cache2.v, H, KV, hd, partials=pieces)
+    src2 = exact[:T].cpu().view(T, H + 2 * KV, hd)
+    _close(y[:T].view(T, H + 2 * KV, hd)[:, :H], _ref_rope(src2[:, :H], p, invc, rot), dtype, "rotated q from pieces",
+           scale=float(src.abs().max()))
+    o = 0
+    for sl, st, n in zip(slots, starts, lens):
+        _close(cache2.rows("k", sl, st + n)[st:], _ref_rope(src2[:, H:H + KV], p, invc, rot)[o:o + n], dtype,
+               f"keys of slot {sl} from pieces", scale=float(src.abs().max()))
+        _close(cache2.rows("v", sl, st + n)[st:], src2[:, H + KV:][o:o + n], dtype, f"values of slot {sl} from pieces",
+               scale=float(src.abs().max()))
+        o += n
 
 
 def _fill_cache(cache, slot, k, v):

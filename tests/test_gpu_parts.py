@@ -22,6 +22,11 @@ def _runtime(dtype):
     return Runtime(device=DEV, dtype=DT[dtype])
 
 
+def _dense(t):
+    """A part may return float32 partial sums [S, n, hidden]; their sum is the result."""
+    return t.sum(dim=0) if t.dim() == 3 else t
+
+
 def _step_for(engine, slots_tokens):
     """A StepContext through the engine's own packing (slots_tokens: [(slot, n_tokens)])."""
     from kuiperllama_b200.engine import SequenceInput
@@ -74,7 +79,7 @@ def test_feed_forward_part(dtype):
     pw = {"P.mlp.gate_proj.weight": w["P.g.weight"].float(), "P.mlp.up_proj.weight": w["P.u.weight"].float(),
           "P.mlp.down_proj.weight": w["P.d.weight"].float()}
     ref = plain_llama.swiglu_feed_forward(x.float().cpu(), pw, "P.")
-    assert_close(part.forward(x, None), ref, dtype, "SwiGLU part")
+    assert_close(_dense(part.forward(x, None)), ref, dtype, "SwiGLU part")
 
 
 def _attention_weights(hid, H, KV, hd, seed):
@@ -115,16 +120,16 @@ def test_attention_part_whole_and_token_by_token(dtype, H, KV, hd):
     with torch.inference_mode():
         slot = cache.alloc_slot()
         step = _step_for(engine, [(slot, T)])
-        whole = mixer.forward(x, step, cache.view(0))
+        whole = _dense(mixer.forward(x, step, cache.view(0)))
         cache.free_slot(slot)
         slot = cache.alloc_slot()
         parts = []
         step = _step_for(engine, [(slot, T - 10)])
-        parts.append(mixer.forward(x[:T - 10].contiguous(), step, cache.view(0)))
+        parts.append(_dense(mixer.forward(x[:T - 10].contiguous(), step, cache.view(0))).float())
         cache.lengths[slot] = T - 10
         for t in range(T - 10, T):
             step = _step_for(engine, [(slot, 1)])
-            parts.append(mixer.forward(x[t:t + 1].contiguous(), step, cache.view(0)))
+            parts.append(_dense(mixer.forward(x[t:t + 1].contiguous(), step, cache.view(0))).float())
             cache.lengths[slot] = t + 1
         cache.free_slot(slot)
     assert_close(whole, ref, dtype, "attention part, whole")
