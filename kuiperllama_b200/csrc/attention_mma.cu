@@ -1,0 +1,364 @@
+// Causal grouped-query attention over the paged cache on the tensor cores (bfloat16 operands,
+// float32 scores, softmax and accumulation): the prefill kernel of the bfloat16 path, and its
+// decode kernel for large batches.
+//
+// Per head: s_t = (q . k_t) * scale for lo <= t <= pos, softmax with the maximum subtracted,
+// o = sum p_t v_t (ExiledOfCode/KuiperLLama mha_kernel.cu:61,74-106: there one CTA per head,
+// one token, scalar FMAs, scores through global memory).
+//
+// A CTA owns 16 * WM query rows of one sequence and one kv head; a row is (token, head of the
+// kv group), so the group's heads share every key and value that is loaded.  Keys and values
+// come a cache page (64 keys) at a time through cp.async into shared memory, double
+// buffered and XOR-swizzled so that ldmatrix is free of bank conflicts.  Each warp keeps its
+// 16 rows' queries as mma.sync A fragments, multiplies them with the page's keys (B fragments
+// by ldmatrix), runs the online softmax on the score fragments in registers, and multiplies
+// the probabilities (converted in place to A fragments) with the values (ldmatrix.trans).
+// With WN > 1 (decode: few rows) the warps of a CTA split each page's keys instead of the
+// rows and merge their results in shared memory; with splits > 1 the pages of a sequence are
+// cut over blockIdx.z and a second kernel merges the pieces.
+#include "common.cuh"
+
+namespace kl {
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+// D (16x8, float32) += A (16x16, bf16, row) * B (16x8, bf16, col)
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// A page of one kv head, [64 keys][HD], into a swizzled stage: the 16-byte chunk c of key row r
+// lands at chunk c ^ (r & 7) of that row.
+template <int HD, int THREADS>
+__device__ __forceinline__ void load_page(bf16* stage, const bf16* __restrict__ src) {
+    constexpr int CHUNKS = HD / 8;                       // 16-byte chunks per row
+    for (int i = threadIdx.x; i < PAGE * CHUNKS; i += THREADS) {
+        const int r = i / CHUNKS, c = i % CHUNKS;
+        cp_async16(stage + r * HD + ((c ^ (r & 7)) << 3), src + r * HD + (c << 3));
+    }
+}
+
+template <int HD, int WM, int WN>
+__global__ void __launch_bounds__(32 * WM * WN)
+attention_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out,
+                     const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
+                     const int* __restrict__ block_table, int blocks_per_seq,
+                     const int* __restrict__ cu_tokens, const int* __restrict__ seq_slots,
+                     const int* __restrict__ seq_starts, const int* __restrict__ seq_new,
+                     float* __restrict__ part_o, float* __restrict__ part_ml,
+                     int H, int KV, int Gp, float scale_log2, int window, int S) {
+    constexpr int THREADS = 32 * WM * WN;
+    constexpr int ROWS = 16 * WM;
+    constexpr int KPW = PAGE / WN;                       // keys of a page that one warp handles
+    constexpr int NT = KPW / 8;                          // score tiles (8 keys each) per warp
+    constexpr int KS = HD / 16;                          // k steps of q . k
+    constexpr int ON = HD / 8;                           // output tiles (8 dims each)
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    bf16* k_stage = reinterpret_cast<bf16*>(smem_raw);                   // [2][64][HD]
+    bf16* v_stage = k_stage + 2 * PAGE * HD;                             // [2][64][HD]
+
+    const int b = blockIdx.y;
+    const int g = blockIdx.z % KV, z = blockIdx.z / KV;
+    const int G = H / KV;
+    const int BT = ROWS / Gp;                            // tokens per CTA
+    const int T = seq_new[b];
+    const int t0 = blockIdx.x * BT;
+    if (t0 >= T) return;
+    const int start = seq_starts[b], slot = seq_slots[b], row0 = cu_tokens[b];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int warp_m = warp % WM, warp_n = warp / WM;
+    const int quad = lane >> 2, tq = lane & 3;
+
+    // this thread's two rows (quad and quad + 8 of the warp's 16)
+    int tok[2], head[2], pos[2], lo[2];
+    bool valid[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int r = warp_m * 16 + quad + 8 * i;
+        const int tl = t0 + r / Gp, hh = r % Gp;
+        valid[i] = tl < T && hh < G;
+        tok[i] = row0 + tl;
+        head[i] = g * G + hh;
+        pos[i] = valid[i] ? start + tl : -1;
+        lo[i] = (window > 0 && valid[i]) ? max(0, pos[i] - window + 1) : 0;
+    }
+    // query fragments
+    uint32_t qa[KS][4];
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            uint32_t x0 = 0u, x1 = 0u;
+            if (valid[i]) {
+                const bf16* p = q + (size_t)tok[i] * q_stride + (size_t)head[i] * HD + ks * 16 + 2 * tq;
+                x0 = *reinterpret_cast<const uint32_t*>(p);
+                x1 = *reinterpret_cast<const uint32_t*>(p + 8);
+            }
+            qa[ks][i] = x0;
+            qa[ks][2 + i] = x1;
+        }
+    }
+    float o[ON][4];
+#pragma unroll
+    for (int n = 0; n < ON; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+
+    // pages this CTA reads
+    const int last_tok = min(T, t0 + BT) - 1;
+    const int max_pos = start + last_tok;
+    const int min_lo = window > 0 ? max(0, start + t0 - window + 1) : 0;
+    const int first_page = min_lo / PAGE, n_pages = max_pos / PAGE - first_page + 1;
+    const int per = (n_pages + S - 1) / S;
+    const int p_begin = first_page + z * per, p_end = min(first_page + n_pages, p_begin + per);
+    const int* table = block_table + (size_t)slot * blocks_per_seq;
+    const int full_below = start + t0;                   // keys <= this are visible to every valid row (no window)
+
+    auto issue = [&](int page_idx, int st) {
+        const size_t off = ((size_t)table[page_idx] * KV + g) * PAGE * HD;
+        load_page<HD, THREADS>(k_stage + st * PAGE * HD, k_cache + off);
+        load_page<HD, THREADS>(v_stage + st * PAGE * HD, v_cache + off);
+        cp_async_commit();
+    };
+    if (p_begin < p_end) issue(p_begin, 0);
+    for (int pi = p_begin; pi < p_end; ++pi) {
+        const int st = (pi - p_begin) & 1;
+        if (pi + 1 < p_end) { issue(pi + 1, st ^ 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
+        __syncthreads();
+        const bf16* ks_ = k_stage + st * PAGE * HD;
+        const bf16* vs_ = v_stage + st * PAGE * HD;
+        const int key0 = pi * PAGE + warp_n * KPW;       // first key of this warp's share
+        float s[NT][4];
+#pragma unroll
+        for (int n = 0; n < NT; ++n) { s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f; }
+        if (key0 <= max_pos) {                           // the warp's keys are not all in the future
+#pragma unroll
+            for (int ks = 0; ks < KS; ++ks) {
+#pragma unroll
+                for (int n2 = 0; n2 < NT / 2; ++n2) {
+                    const int r = warp_n * KPW + n2 * 16 + (lane & 7) + ((lane >> 4) << 3);
+                    const int c = ks * 2 + ((lane >> 3) & 1);
+                    uint32_t b0, b1, b2, b3;
+                    ldmatrix_x4(smem_addr(ks_ + r * HD + ((c ^ (r & 7)) << 3)), b0, b1, b2, b3);
+                    mma_bf16(s[2 * n2], qa[ks], b0, b1);
+                    mma_bf16(s[2 * n2 + 1], qa[ks], b2, b3);
+                }
+            }
+            // scale, mask, online softmax
+            const bool need_mask = key0 + KPW - 1 > full_below || window > 0 || !valid[0] || !valid[1];
+            float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+            for (int n = 0; n < NT; ++n) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const int i = c >> 1;
+                    float v = s[n][c] * scale_log2;
+                    if (need_mask) {
+                        const int kp = key0 + n * 8 + 2 * tq + (c & 1);
+                        if (kp > pos[i] || kp < lo[i]) v = -INFINITY;
+                    }
+                    s[n][c] = v;
+                    mx[i] = fmaxf(mx[i], v);
+                }
+            }
+            float corr[2], muse[2];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
+                mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
+                const float m_new = fmaxf(m[i], mx[i]);
+                muse[i] = m_new == -INFINITY ? 0.f : m_new;
+                corr[i] = exp2f(m[i] - muse[i]);         // 0 when nothing was seen before
+                m[i] = m_new;
+                l[i] *= corr[i];
+            }
+#pragma unroll
+            for (int n = 0; n < ON; ++n) { o[n][0] *= corr[0]; o[n][1] *= corr[0]; o[n][2] *= corr[1]; o[n][3] *= corr[1]; }
+#pragma unroll
+            for (int n = 0; n < NT; ++n) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const float p = exp2f(s[n][c] - muse[c >> 1]);
+                    s[n][c] = p;
+                    l[c >> 1] += p;
+                }
+            }
+            // probabilities as A fragments, times the values
+#pragma unroll
+            for (int kk = 0; kk < KPW / 16; ++kk) {
+                uint32_t pa[4];
+                pa[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+                pa[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+                pa[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+                pa[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+                for (int n2 = 0; n2 < ON / 2; ++n2) {
+                    const int r = warp_n * KPW + kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
+                    const int c = n2 * 2 + (lane >> 4);
+                    uint32_t b0, b1, b2, b3;
+                    ldmatrix_x4_trans(smem_addr(vs_ + r * HD + ((c ^ (r & 7)) << 3)), b0, b1, b2, b3);
+                    mma_bf16(o[2 * n2], pa, b0, b1);
+                    mma_bf16(o[2 * n2 + 1], pa, b2, b3);
+                }
+            }
+        }
+        __syncthreads();                                 // the stage may be overwritten by the next prefetch
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
+        l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
+    }
+    if constexpr (WN > 1) {
+        // merge the warps that shared the rows: through shared memory (the stages are free now)
+        float* sm_m = reinterpret_cast<float*>(smem_raw);            // [WN][ROWS]
+        float* sm_l = sm_m + WN * ROWS;                              // [WN][ROWS]
+        float* sm_o = sm_l + WN * ROWS;                              // [WN][ROWS][HD]
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int r = warp_m * 16 + quad + 8 * i;
+            if (tq == 0) { sm_m[warp_n * ROWS + r] = m[i]; sm_l[warp_n * ROWS + r] = l[i]; }
+#pragma unroll
+            for (int n = 0; n < ON; ++n) {
+                sm_o[((size_t)warp_n * ROWS + r) * HD + n * 8 + 2 * tq] = o[n][2 * i];
+                sm_o[((size_t)warp_n * ROWS + r) * HD + n * 8 + 2 * tq + 1] = o[n][2 * i + 1];
+            }
+        }
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < ROWS * HD; idx += THREADS) {
+            const int r = idx / HD, d = idx % HD;
+            const int tl = t0 + r / Gp, hh = r % Gp;
+            if (tl >= T || hh >= G) continue;
+            float M = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < WN; ++w) M = fmaxf(M, sm_m[w * ROWS + r]);
+            float L = 0.f, acc = 0.f;
+#pragma unroll
+            for (int w = 0; w < WN; ++w) {
+                const float mw = sm_m[w * ROWS + r];
+                const float c = mw == -INFINITY ? 0.f : exp2f(mw - M);
+                L += sm_l[w * ROWS + r] * c;
+                acc += sm_o[((size_t)w * ROWS + r) * HD + d] * c;
+            }
+            const size_t orow = (size_t)(row0 + tl) * H + (g * G + hh);
+            if (S == 1) out[orow * HD + d] = __float2bfloat16_rn(acc / L);
+            else {
+                part_o[(orow * S + z) * HD + d] = acc;
+                if (d == 0) { part_ml[(orow * S + z) * 2] = M; part_ml[(orow * S + z) * 2 + 1] = L; }
+            }
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            if (!valid[i]) continue;
+            const size_t orow = (size_t)tok[i] * H + head[i];
+            if (S == 1) {
+                const float inv = 1.f / l[i];
+#pragma unroll
+                for (int n = 0; n < ON; ++n)
+                    *reinterpret_cast<uint32_t*>(out + orow * HD + n * 8 + 2 * tq) = pack_bf16(o[n][2 * i] * inv, o[n][2 * i + 1] * inv);
+            } else {
+#pragma unroll
+                for (int n = 0; n < ON; ++n)
+                    *reinterpret_cast<float2*>(part_o + (orow * S + z) * HD + n * 8 + 2 * tq) = make_float2(o[n][2 * i], o[n][2 * i + 1]);
+                if (tq == 0) { part_ml[(orow * S + z) * 2] = m[i]; part_ml[(orow * S + z) * 2 + 1] = l[i]; }
+            }
+        }
+    }
+}
+
+// Merge the pieces of a split sequence: maxima and sums are in the exp2 domain of the kernel above.
+template <int HD>
+__global__ void attention_mma_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                             bf16* __restrict__ out, int H, int S) {
+    const size_t orow = (size_t)blockIdx.x * H + blockIdx.y;
+    float M = -INFINITY;
+    for (int z = 0; z < S; ++z) M = fmaxf(M, part_ml[(orow * S + z) * 2]);
+    for (int d = threadIdx.x; d < HD; d += blockDim.x) {
+        float L = 0.f, acc = 0.f;
+        for (int z = 0; z < S; ++z) {
+            const float mz = part_ml[(orow * S + z) * 2];
+            const float c = mz == -INFINITY ? 0.f : exp2f(mz - M);
+            L += part_ml[(orow * S + z) * 2 + 1] * c;
+            acc += part_o[(orow * S + z) * HD + d] * c;
+        }
+        out[orow * HD + d] = __float2bfloat16_rn(acc / L);
+    }
+}
+
+template <int HD, int WM, int WN>
+static int launch_mma(const bf16* q, int q_stride, bf16* out, const bf16* k, const bf16* v, const int* table, int bps,
+                      const int* cu, const int* slots, const int* starts, const int* news, float* po, float* pml,
+                      int n_seqs, int max_new, int n_rows, int H, int KV, float scale, int window, int S,
+                      cudaStream_t stream) {
+    const int G = H / KV;
+    int Gp = 1;
+    while (Gp < G) Gp <<= 1;
+    constexpr int ROWS = 16 * WM;
+    if (Gp > ROWS) return KL_ERR_BAD_SIZE;
+    const int BT = ROWS / Gp;
+    const dim3 grid((max_new + BT - 1) / BT, n_seqs, KV * S);
+    if (grid.y > 65535 || grid.z > 65535) return KL_ERR_BAD_SIZE;
+    size_t smem = (size_t)4 * PAGE * HD * sizeof(bf16);
+    if (WN > 1) smem = max(smem, (size_t)(2 * WN * ROWS + WN * ROWS * HD) * sizeof(float));
+    static bool configured = false;
+    if (!configured) {
+        KL_CUDA(cudaFuncSetAttribute(attention_mma_kernel<HD, WM, WN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured = true;
+    }
+    attention_mma_kernel<HD, WM, WN><<<grid, 32 * WM * WN, smem, stream>>>(q, q_stride, out, k, v, table, bps, cu, slots,
+        starts, news, po, pml, H, KV, Gp, scale * 1.4426950408889634f, window, S);
+    KL_LAUNCH_CHECK();
+    if (S > 1) {
+        attention_mma_combine_kernel<HD><<<dim3(n_rows, H), HD <= 64 ? 32 : 64, 0, stream>>>(po, pml, out, H, S);
+        KL_LAUNCH_CHECK();
+    }
+    return KL_OK;
+}
+
+}  // namespace kl
+
+using namespace kl;
+
+// Attention of a ragged batch: sequence b brings seq_new[b] tokens (rows cu_tokens[b] ... of q
+// and out) that start at position seq_starts[b] of slot seq_slots[b]; its keys and values are
+// already in the cache.  max_new is the largest seq_new (host copy, sizes the grid); n_rows the
+// number of packed rows.  few_rows != 0 picks the layout for decode (one token per sequence:
+// the warps of a CTA split the keys).  Head sizes 64 and 128; others KL_ERR_BAD_SIZE.
+KL_API int kl_attention_mma(const void* q, int q_stride, void* out, const void* k_cache, const void* v_cache,
+                            const int* block_table, int blocks_per_seq, const int* cu_tokens, const int* seq_slots,
+                            const int* seq_starts, const int* seq_new, float* part_o, float* part_ml, int n_seqs,
+                            int max_new, int n_rows, int H, int KV, int hd, float scale, int window, int splits,
+                            int few_rows, cudaStream_t stream) {
+    if (n_seqs <= 0 || max_new <= 0) return KL_OK;
+    if (KV <= 0 || H % KV || splits < 1) return KL_ERR_BAD_SIZE;
+    if (splits > 1 && (part_o == nullptr || part_ml == nullptr)) return KL_ERR_BAD_SIZE;
+    if (q_stride % 2 || ((uintptr_t)q & 3)) return KL_ERR_BAD_ALIGN;
+#define KL_MMA(HD, WM, WN)                                                                                            \
+    return launch_mma<HD, WM, WN>((const bf16*)q, q_stride, (bf16*)out, (const bf16*)k_cache, (const bf16*)v_cache,     \
+                                  block_table, blocks_per_seq, cu_tokens, seq_slots, seq_starts, seq_new, part_o,      \
+                                  part_ml, n_seqs, max_new, n_rows, H, KV, scale, window, splits, stream)
+    if (hd == 128) { if (few_rows) KL_MMA(128, 1, 4); else KL_MMA(128, 4, 1); }
+    if (hd == 64) { if (few_rows) KL_MMA(64, 1, 4); else KL_MMA(64, 4, 1); }
+#undef KL_MMA
+    return KL_ERR_BAD_SIZE;
+}

@@ -29,6 +29,7 @@ SOURCES: Dict[str, str] = {
     "rope_kv": "rope_kv.cu",
     "attention_simt": "attention_simt.cu",
     "attention_decode": "attention_decode.cu",
+    "attention_mma": "attention_mma.cu",
     "gemm_simt": "gemm_simt.cu",
     "gemm_tcgen05": "gemm_tcgen05.cu",
     "sampling": "sampling.cu",

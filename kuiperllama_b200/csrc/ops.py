@@ -404,12 +404,59 @@ def attention_decode(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache:
         ctypes.c_float(scale), int(window or 0), splits, _stream()), "attention_decode", 2 if splits > 1 else 1)
 
 
+MMA_HEAD_DIMS = (64, 128)
+
+
+def attention_mma(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                  block_table: torch.Tensor, cu_tokens: torch.Tensor, seq_slots: torch.Tensor, seq_starts: torch.Tensor,
+                  seq_new: torch.Tensor, n_seqs: int, max_new: int, n_rows: int, num_heads: int, num_kv_heads: int,
+                  head_dim: int, scale: float, window: int = 0, splits: int = 1, few_rows: bool = False) -> None:
+    """Tensor-core attention of a ragged batch over the paged cache (bfloat16, head sizes 64
+    and 128).  ``few_rows``: the layout for one token per sequence; ``splits``: pieces each
+    sequence's pages are cut into."""
+    _cuda(q, out, k_cache, v_cache, block_table, cu_tokens, seq_slots, seq_starts, seq_new)
+    for t, nm in ((block_table, "block_table"), (cu_tokens, "cu_tokens"), (seq_slots, "seq_slots"),
+                  (seq_starts, "seq_starts"), (seq_new, "seq_new")):
+        _i32(t, nm)
+    _need(q.dtype == out.dtype == k_cache.dtype == v_cache.dtype == torch.bfloat16, "attention_mma: bfloat16 only")
+    _need(head_dim in MMA_HEAD_DIMS, f"attention_mma: head_dim {head_dim} not in {MMA_HEAD_DIMS}")
+    _need(out.is_contiguous() and out.shape[0] >= n_rows and out.shape[1] == num_heads * head_dim, "attention_mma: out shape")
+    _need(k_cache.is_contiguous() and v_cache.is_contiguous()
+          and tuple(k_cache.shape[1:]) == (num_kv_heads, PAGE, head_dim), "attention_mma: cache layout")
+    _need(num_heads % num_kv_heads == 0 and num_heads // num_kv_heads <= 16, "attention_mma: group size up to 16")
+    po = pml = None
+    if splits > 1:
+        po = torch.empty((n_rows, num_heads, splits, head_dim), dtype=torch.float32, device=q.device)
+        pml = torch.empty((n_rows, num_heads, splits, 2), dtype=torch.float32, device=q.device)
+    _check(lib("attention_mma").kl_attention_mma(
+        _ptr(q), q_stride, _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1],
+        _ptr(cu_tokens), _ptr(seq_slots), _ptr(seq_starts), _ptr(seq_new), _ptr(po), _ptr(pml), n_seqs, max_new, n_rows,
+        num_heads, num_kv_heads, head_dim, ctypes.c_float(scale), int(window or 0), splits, int(few_rows), _stream()),
+        "attention_mma", 2 if splits > 1 else 1)
+
+
+# Which kernel decode steps of the bfloat16 path use when both fit: "mma" (tensor cores) or
+# "simt" (attention_decode.cu).
+DECODE_KERNEL = "mma"
+
+
 def attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
               block_table: torch.Tensor, step, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
               window: int = 0) -> None:
-    """Attention of every token of ``step`` over its sequence's cache.  bfloat16 decode steps
-    (one token per sequence) take the split-KV kernel; everything else the plain kernel."""
-    if step.is_decode and q.dtype == torch.bfloat16 and head_dim in DECODE_HEAD_DIMS and q_stride % 8 == 0:
+    """Attention of every token of ``step`` over its sequence's cache.  The bfloat16 path
+    takes the tensor-core kernel (head sizes 64 and 128) or, for decode steps with other head
+    sizes, the split-KV kernel; float32 and everything else takes the plain kernel."""
+    bf = q.dtype == torch.bfloat16
+    group = num_heads // num_kv_heads
+    if bf and head_dim in MMA_HEAD_DIMS and group <= 16 and (not step.is_decode or DECODE_KERNEL == "mma"):
+        splits = 1
+        if step.is_decode:
+            ctas = max(1, step.n_seqs * num_kv_heads)
+            splits = max(1, min(16, (2 * SM_COUNT + ctas - 1) // ctas))
+        attention_mma(q, q_stride, out, k_cache, v_cache, block_table, step.cu_tokens, step.seq_slots, step.seq_starts,
+                      step.seq_new, step.n_seqs, step.max_new, step.n_tokens, num_heads, num_kv_heads, head_dim, scale,
+                      window, splits, few_rows=step.is_decode)
+    elif bf and step.is_decode and head_dim in DECODE_HEAD_DIMS and q_stride % 8 == 0:
         attention_decode(q, q_stride, out, k_cache, v_cache, block_table, step.positions, step.token_slot, step.n_tokens,
                          num_heads, num_kv_heads, head_dim, scale, window)
     else:

@@ -33,7 +33,13 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const float* __restric
     auto value = [&](int idx) {                             // element idx of this token's q|k|v row, in float32
         if (prow == nullptr) return to_f32(row[idx]);
         float a = 0.f;
-        for (int z = 0; z < n_partials; ++z) a += prow[(size_t)z * partial_stride + idx];
+        int z = 0;
+        for (; z + 4 <= n_partials; z += 4) {               // four loads in flight, added in ascending order
+            const float p0 = prow[(size_t)z * partial_stride + idx], p1 = prow[(size_t)(z + 1) * partial_stride + idx];
+            const float p2 = prow[(size_t)(z + 2) * partial_stride + idx], p3 = prow[(size_t)(z + 3) * partial_stride + idx];
+            a = (((a + p0) + p1) + p2) + p3;
+        }
+        for (; z < n_partials; ++z) a += prow[(size_t)z * partial_stride + idx];
         return a;
     };
     const int half = hd / 2;                                // work items per head: hd/2 pairs of lanes
@@ -48,38 +54,42 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const float* __restric
         prow = nullptr;
         __syncthreads();
     }
-    // queries and keys: (head, j) with j in [0, hd/2): element j and element j + hd/2 are
-    // handled together so that each thread owns what it reads and writes.
+    // Full rotation (the usual case): the CTAs of a token (gridDim.y of them) share its work
+    // items, first the (head, j) pairs of queries and keys (element j and element j + hd/2 are
+    // handled together, so each thread owns what it reads and writes), then the value elements.
     const int n_qk = (H + KV) * half;
-    for (int idx = threadIdx.x; idx < n_qk; idx += blockDim.x) {
-        const int head = idx / half;
-        const int j = idx - head * half;
-        T* h = row + (size_t)head * hd;
-        // the two elements this thread owns
-        const int e0 = j, e1 = j + half;
-        if (rot != hd) break;                               // handled below
-        float v0 = value(head * hd + e0), v1 = value(head * hd + e1);
-        if (rot == hd) {
-            float s, c;
-            sincosf((float)pos * inv_freq[j], &s, &c);
-            const float a = v0, b = v1;
-            v0 = a * c - b * s;
-            v1 = b * c + a * s;
-            if (head < H) {
-                h[e0] = from_f32<T>(v0);
-                h[e1] = from_f32<T>(v1);
+    if (rot == hd) {
+        const int total = n_qk + (write_kv ? KV * hd : 0);
+        for (int w = blockIdx.y * blockDim.x + threadIdx.x; w < total; w += gridDim.y * blockDim.x) {
+            if (w < n_qk) {
+                const int head = w / half;
+                const int j = w - head * half;
+                if (head >= H && !write_kv) continue;
+                const float a = value(head * hd + j), b = value(head * hd + j + half);
+                float sn, cs;
+                sincosf((float)pos * inv_freq[j], &sn, &cs);
+                const float v0 = a * cs - b * sn, v1 = b * cs + a * sn;
+                if (head < H) {
+                    T* h = row + (size_t)head * hd;
+                    h[j] = from_f32<T>(v0);
+                    h[j + half] = from_f32<T>(v1);
+                } else {
+                    T* dst = k_cache + cache_row_offset(block_table, blocks_per_seq, slot, pos, head - H, KV, hd);
+                    dst[j] = from_f32<T>(v0);
+                    dst[j + half] = from_f32<T>(v1);
+                }
+            } else {
+                const int idx = w - n_qk;
+                const int g = idx / hd, e = idx - g * hd;
+                T* dst = v_cache + cache_row_offset(block_table, blocks_per_seq, slot, pos, g, KV, hd);
+                dst[e] = from_f32<T>(value((H + KV) * hd + idx));
             }
         }
-        if (head >= H && write_kv && rot == hd) {
-            const int g = head - H;
-            T* dst = k_cache + cache_row_offset(block_table, blocks_per_seq, slot, pos, g, KV, hd);
-            dst[e0] = from_f32<T>(v0);
-            dst[e1] = from_f32<T>(v1);
-        }
+        return;
     }
-    if (rot != hd) {
-        // Partial or absent rotation: pairs (j, j + rot/2) for j < rot/2; the rest passes through.
-        __syncthreads();
+    {
+        // Partial or absent rotation (one CTA per token): pairs (j, j + rot/2) for j < rot/2; the
+        // rest passes through.
         const int n_pairs = (H + KV) * rhalf;
         for (int idx = threadIdx.x; idx < n_pairs; idx += blockDim.x) {
             const int head = idx / rhalf;
@@ -122,14 +132,16 @@ KL_API int kl_rope_kv_write(void* qkv, const float* partials, int n_partials, lo
     if (hd % 2 || rotary_dim % 2 || rotary_dim > hd || rotary_dim < 0) return KL_ERR_BAD_SIZE;
     if (rotary_dim > 0 && inv_freq == nullptr) return KL_ERR_BAD_SIZE;
     if (n_partials < 0 || (n_partials > 0 && partials == nullptr)) return KL_ERR_BAD_SIZE;
-    const int work = (H + KV) * hd / 2;
-    const int threads = work >= 2048 ? 512 : (work >= 1024 ? 256 : (work >= 256 ? 128 : 64));
+    const int work = (H + KV) * hd / 2 + (write_kv ? KV * hd : 0);
+    const int threads = work >= 1024 ? 256 : (work >= 256 ? 128 : 64);
+    // full rotation: a token's work is spread over several CTAs (one item per thread)
+    const int ctas = rotary_dim == hd ? (work + threads - 1) / threads : 1;
     if (dtype == KL_F32)
-        rope_kv_write_kernel<float><<<n_tokens, threads, 0, stream>>>((float*)qkv, partials, n_partials,
+        rope_kv_write_kernel<float><<<dim3(n_tokens, ctas), threads, 0, stream>>>((float*)qkv, partials, n_partials,
             (size_t)partial_stride, inv_freq, rotary_dim, positions,
             token_slot, block_table, blocks_per_seq, (float*)k_cache, (float*)v_cache, H, KV, hd, write_kv);
     else if (dtype == KL_BF16)
-        rope_kv_write_kernel<bf16><<<n_tokens, threads, 0, stream>>>((bf16*)qkv, partials, n_partials,
+        rope_kv_write_kernel<bf16><<<dim3(n_tokens, ctas), threads, 0, stream>>>((bf16*)qkv, partials, n_partials,
             (size_t)partial_stride, inv_freq, rotary_dim, positions,
             token_slot, block_table, blocks_per_seq, (bf16*)k_cache, (bf16*)v_cache, H, KV, hd, write_kv);
     else

@@ -445,3 +445,87 @@ def test_attention_decode_finds_one_far_key_among_thousands(ops, splits):
         ops.attention_decode(qbuf, H * hd, out, cache.k, cache.v, cache.table, pos, tslot, 1, H, KV, hd, 1 / math.sqrt(hd), 0, splits)
         want = v[far].to(dt).float().repeat_interleave(H // KV, dim=0)
         _close(out.view(H, hd), want, "bfloat16", f"far key at {far}, {splits} splits")
+
+
+# ----------------------------------------------------------------------------- tensor-core attention
+
+def _ragged_problem(H, KV, hd, seqs, seed):
+    """seqs: [(start, new)] per sequence.  Fills the cache with start + new keys per sequence."""
+    torch.manual_seed(seed)
+    dt = torch.bfloat16
+    n = len(seqs)
+    cache = Paged(n + 1, max(s + t for s, t in seqs) + 1, KV, hd, dt, seed=seed)
+    slots = list(range(n, 0, -1))
+    ks = [torch.randn(s + t, KV, hd) for s, t in seqs]
+    vs = [torch.randn(s + t, KV, hd) for s, t in seqs]
+    for sl, k, v in zip(slots, ks, vs):
+        _fill_cache(cache, sl, k, v)
+    rows = sum(t for _, t in seqs)
+    stride = (H + 2 * KV) * hd
+    qbuf = torch.randn(rows + 2, stride, device=DEV).to(dt)           # two padding rows at the end
+    cu = [0]
+    for _, t in seqs:
+        cu.append(cu[-1] + t)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+    return cache, slots, ks, vs, qbuf, stride, i32(cu), i32(slots), i32([s for s, _ in seqs]), i32([t for _, t in seqs]), rows
+
+
+@pytest.mark.parametrize("H,KV,hd,window", [(8, 2, 128, 0), (4, 4, 64, 0), (6, 2, 64, 0), (32, 8, 128, 0), (8, 1, 128, 0),
+                                            (4, 2, 128, 50), (16, 1, 64, 0)])
+def test_attention_mma_prefill(ops, H, KV, hd, window):
+    seqs = [(0, 150), (0, 1), (60, 70), (3, 64), (0, 65), (100, 5)]
+    cache, slots, ks, vs, qbuf, stride, cu, sl, st, nw, rows = _ragged_problem(H, KV, hd, seqs, seed=15)
+    out = torch.full((rows + 2, H * hd), 3.0, device=DEV, dtype=torch.bfloat16)
+    scale = 1 / math.sqrt(hd)
+    ops.attention_mma(qbuf, stride, out, cache.k, cache.v, cache.table, cu, sl, st, nw, len(seqs), max(t for _, t in seqs),
+                      rows, H, KV, hd, scale, window, 1, False)
+    assert float((out[rows:].float() - 3.0).abs().max()) == 0.0, "a padding row was written"
+    r = 0
+    for i, (s0, t) in enumerate(seqs):
+        kk, vv = ks[i].bfloat16().float(), vs[i].bfloat16().float()
+        for j in range(t):
+            qv = qbuf[r, :H * hd].float().cpu().view(H, hd)
+            ref = _ref_attention(qv, kk, vv, s0 + j, scale, window)
+            _close(out[r].view(H, hd), ref, "bfloat16", f"mma prefill seq {i} token {j}", scale=float(vv.abs().max()))
+            r += 1
+
+
+@pytest.mark.parametrize("H,KV,hd,window,splits", [(8, 2, 128, 0, 1), (32, 8, 128, 0, 5), (4, 4, 64, 0, 3), (6, 2, 64, 0, 16),
+                                                   (8, 8, 128, 100, 2), (16, 1, 128, 0, 4)])
+def test_attention_mma_decode(ops, H, KV, hd, window, splits):
+    seqs = [(199, 1), (0, 1), (64, 1), (128, 1), (63, 1), (249, 1), (1000, 1)]
+    cache, slots, ks, vs, qbuf, stride, cu, sl, st, nw, rows = _ragged_problem(H, KV, hd, seqs, seed=16)
+    out = torch.full((rows + 2, H * hd), 3.0, device=DEV, dtype=torch.bfloat16)
+    scale = 1 / math.sqrt(hd)
+    ops.attention_mma(qbuf, stride, out, cache.k, cache.v, cache.table, cu, sl, st, nw, len(seqs), 1, rows, H, KV, hd, scale,
+                      window, splits, True)
+    for i, (s0, _) in enumerate(seqs):
+        qv = qbuf[i, :H * hd].float().cpu().view(H, hd)
+        ref = _ref_attention(qv, ks[i].bfloat16().float(), vs[i].bfloat16().float(), s0, scale, window)
+        _close(out[i].view(H, hd), ref, "bfloat16", f"mma decode seq {i} (len {s0 + 1})", scale=float(vs[i].abs().max()))
+
+
+@pytest.mark.parametrize("few_rows,splits", [(False, 1), (True, 1), (True, 7)])
+def test_attention_mma_finds_one_far_key_among_thousands(ops, few_rows, splits):
+    torch.manual_seed(17)
+    dt = torch.bfloat16
+    H, KV, hd, n = 8, 2, 128, 3000
+    for far in (0, 63, 64, 1999, 2999):
+        cache = Paged(2, 3072, KV, hd, dt, seed=6)
+        k = torch.randn(n, KV, hd) * 0.1
+        v = torch.randn(n, KV, hd)
+        k[far] = 0
+        k[far, :, 9] = 40.0
+        _fill_cache(cache, 1, k, v)
+        new = 1 if few_rows else 20                                  # the last `new` tokens are the queries
+        q = torch.randn(new, H, hd) * 0.1
+        q[:, :, 9] = 40.0
+        qbuf = q.view(new, H * hd).to(dt).to(DEV)
+        out = torch.empty(new, H * hd, device=DEV, dtype=dt)
+        i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+        ops.attention_mma(qbuf, H * hd, out, cache.k, cache.v, cache.table, i32([0, new]), i32([1]), i32([n - new]), i32([new]),
+                          1, new, new, H, KV, hd, 1 / math.sqrt(hd), 0, splits, few_rows)
+        want = v[far].to(dt).float().repeat_interleave(H // KV, dim=0)
+        for j in range(new):
+            if far <= n - new + j:
+                _close(out[j].view(H, hd), want, "bfloat16", f"far key at {far}, query {j}")
