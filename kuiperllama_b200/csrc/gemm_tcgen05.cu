@@ -139,7 +139,26 @@ struct GemmArgs {
     int k_blocks;       // ceil(K / 64)
     int out_f32;        // 1: float32 output, 0: bfloat16
     int* status;        // device status word, 0 = fine
+    int tiles_m;        // tokens-as-rows: tiles along the tokens and along the output features;
+    int tiles_n;        //   blockIdx.x walks them in groups of TC_GROUP_M token tiles (see tile_of)
+    int swiglu;         // 1: the B (or A) operand's rows alternate 64 gate rows and 64 up rows; the
+                        //    epilogue writes silu(gate) * up, half as many output features, bf16
 };
+
+// Tile order for tokens-as-rows: all the feature tiles of a group of TC_GROUP_M token tiles
+// before the next group, token tiles fastest.  CTAs that run at the same time then share a few
+// weight tiles and a few token tiles, and both stay in L2 instead of being streamed from HBM
+// once per token tile.
+constexpr int TC_GROUP_M = 16;
+__device__ __forceinline__ void tile_of(int id, int tiles_m, int tiles_n, int& tm, int& tn) {
+    const int per_group = TC_GROUP_M * tiles_n;
+    const int group = id / per_group, in = id - group * per_group;
+    const int first = group * TC_GROUP_M;
+    const int gm = min(TC_GROUP_M, tiles_m - first);
+    tm = first + in % gm;
+    tn = in / gm;
+}
+__device__ __forceinline__ float silu_mul(float g, float u) { return g * (1.0f / (1.0f + __expf(-g))) * u; }
 
 template <int BN, int STAGES, bool WEIGHT_ROWS>
 __global__ void __launch_bounds__(TC_THREADS, 1)
@@ -157,8 +176,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tile_a = WEIGHT_ROWS ? blockIdx.x : blockIdx.y;          // tile index along the A operand's rows
-    const int tile_b = WEIGHT_ROWS ? 0 : blockIdx.x;
+    int tile_a, tile_b;                                                // tile index along the A / B operand's rows
+    if constexpr (WEIGHT_ROWS) { tile_a = blockIdx.x; tile_b = 0; }
+    else tile_of(blockIdx.x, args.tiles_m, args.tiles_n, tile_a, tile_b);
     // k range of this CTA (cut over blockIdx.z)
     const int per = (args.k_blocks + gridDim.z - 1) / gridDim.z;
     const int kb0 = blockIdx.z * per;
@@ -218,12 +238,53 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     } else {
         // ---------------------------------------------------------------- epilogue: warps 2..5
         const int quarter = warp & 3;                         // the 32 tensor-memory lanes this warp may read
-        const bool ok = mbar_wait(acc_ready, 0, abort_flag, args.status, 3);
+        const bool ok = mbar_wait(acc_ready, 0, abort_flag, args.status, 3) && !*abort_flag;
         tc_fence_after();
-        if (ok && !*abort_flag) {
-            const int row = tile_a * TC_BM + quarter * 32 + lane;          // row of the A operand
-            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
-            if constexpr (WEIGHT_ROWS) {
+        const int row = tile_a * TC_BM + quarter * 32 + lane;              // row of the A operand
+        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        if constexpr (WEIGHT_ROWS) {
+            if (args.swiglu) {
+                // Tile rows 0..63 are gate features, 64..127 the up rows of the same features.  The
+                // warps that hold the up rows pass them through shared memory (the stages are
+                // free: every MMA has read them) to the warps that hold the gate rows.
+                float* xch = reinterpret_cast<float*>(tiles_a);            // [BN tokens][64 features]
+                const int f = (quarter & 1) * 32 + lane;                   // feature within the tile
+                uint32_t r[16];
+                if (ok && quarter >= 2) {
+#pragma unroll
+                    for (int c = 0; c < BN; c += 16) {
+                        if (nkb > 0) { tmem_ld16(taddr + c, r); tmem_ld_wait(); }
+                        else {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) r[j] = 0u;
+                        }
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) xch[(c + j) * 64 + f] = __uint_as_float(r[j]);
+                    }
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");             // the four epilogue warps, whatever happened
+                if (ok && quarter < 2) {
+                    const int feature = tile_a * 64 + f;
+                    __nv_bfloat16* outb = (__nv_bfloat16*)args.out;
+#pragma unroll
+                    for (int c = 0; c < BN; c += 16) {
+                        if (nkb > 0) { tmem_ld16(taddr + c, r); tmem_ld_wait(); }
+                        else {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) r[j] = 0u;
+                        }
+                        if (feature < args.rows_a / 2) {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) {
+                                const int m = c + j;
+                                if (m < args.rows_b)
+                                    outb[(size_t)m * args.ld_out + feature] =
+                                        __float2bfloat16_rn(silu_mul(__uint_as_float(r[j]), xch[m * 64 + f]));
+                            }
+                        }
+                    }
+                }
+            } else if (ok) {
                 // tile rows are output features n, tile columns are tokens m: out[z][m][n]
                 float* out = (float*)args.out + (size_t)blockIdx.z * args.split_stride;
                 __nv_bfloat16* outb = (__nv_bfloat16*)args.out;
@@ -243,6 +304,44 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                                 if (args.out_f32) out[(size_t)m * args.ld_out + row] = __uint_as_float(r[j]);
                                 else outb[(size_t)m * args.ld_out + row] = __float2bfloat16_rn(__uint_as_float(r[j]));
                             }
+                        }
+                    }
+                }
+            }
+        } else if (ok) {
+            if (args.swiglu) {
+                // tile columns: 64 gate, 64 up, 64 gate, 64 up -> 128 outputs silu(gate) * up per row
+                uint32_t rg[32], ru[32];
+                const int half_n = args.rows_b / 2;
+#pragma unroll 1
+                for (int c = 0; c < BN / 2; c += 32) {                     // c: output column within the tile
+                    const int f0 = tile_b * (BN / 2) + c;
+                    if (f0 >= half_n) break;
+                    const int col = (c / 64) * 128 + (c % 64);             // gate column in the accumulator
+                    if (nkb > 0) { tmem_ld32(taddr + col, rg); tmem_ld32(taddr + col + 64, ru); tmem_ld_wait(); }
+                    else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) { rg[j] = 0u; ru[j] = 0u; }
+                    }
+                    if (row < args.rows_a) {
+                        __nv_bfloat16* o = (__nv_bfloat16*)args.out + (size_t)row * args.ld_out + f0;
+                        if (f0 + 32 <= half_n && (args.ld_out & 7) == 0) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 8) {
+                                uint32_t w[4];
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) {
+                                    __nv_bfloat162 pr = __floats2bfloat162_rn(
+                                        silu_mul(__uint_as_float(rg[j + 2 * e]), __uint_as_float(ru[j + 2 * e])),
+                                        silu_mul(__uint_as_float(rg[j + 2 * e + 1]), __uint_as_float(ru[j + 2 * e + 1])));
+                                    w[e] = *reinterpret_cast<uint32_t*>(&pr);
+                                }
+                                *reinterpret_cast<uint4*>(o + j) = make_uint4(w[0], w[1], w[2], w[3]);
+                            }
+                        } else {
+                            for (int j = 0; j < 32; ++j)
+                                if (f0 + j < half_n)
+                                    o[j] = __float2bfloat16_rn(silu_mul(__uint_as_float(rg[j]), __uint_as_float(ru[j])));
                         }
                     }
                 }
@@ -390,16 +489,18 @@ using namespace kl;
 // out[M, N] = a[M, K] * w[N, K]^T, tokens as tile rows (any M).  out is bf16 (out_f32 = 0) or
 // float32.  Needs 16-byte aligned bases and row strides (K % 8 == 0): else KL_ERR_BAD_ALIGN.
 KL_API int kl_gemm_tcgen05(const void* a, long long lda, const void* w, long long ldw, void* out, long long ldo, int M,
-                           int N, int K, int out_f32, int* status, cudaStream_t stream) {
+                           int N, int K, int out_f32, int swiglu, int* status, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return KL_OK;
+    if (swiglu && (out_f32 || N % 128)) return KL_ERR_BAD_SIZE;
     if (!aligned_operand(a, lda, K) || !aligned_operand(w, ldw, K)) return KL_ERR_BAD_ALIGN;
     CUtensorMap ma, mb;
     int rc;
     if ((rc = make_map(&ma, a, M, K, lda, TC_BM)) != KL_OK) return rc;
     if ((rc = make_map(&mb, w, N, K, ldw, 256)) != KL_OK) return rc;
-    GemmArgs args{out, ldo, 0, M, N, (K + TC_BK - 1) / TC_BK, out_f32, status};
-    dim3 grid((N + 255) / 256, (M + TC_BM - 1) / TC_BM, 1);
-    if (grid.y > 65535) return KL_ERR_BAD_SIZE;
+    const int tiles_m = (M + TC_BM - 1) / TC_BM, tiles_n = (N + 255) / 256;
+    GemmArgs args{out, ldo, 0, M, N, (K + TC_BK - 1) / TC_BK, out_f32, status, tiles_m, tiles_n, swiglu};
+    if ((long long)tiles_m * tiles_n > 0x7fffffffLL) return KL_ERR_BAD_SIZE;
+    dim3 grid(tiles_m * tiles_n, 1, 1);
     return launch<256, 4, false>(ma, mb, args, grid, stream);
 }
 
@@ -407,9 +508,11 @@ KL_API int kl_gemm_tcgen05(const void* a, long long lda, const void* w, long lon
 // splits == 1: out[M, N] directly (bf16 or float32).  splits > 1: out is float32
 // [splits, M, N] partial sums (out_f32 must be 1) for the caller to add.
 KL_API int kl_gemm_tcgen05_skinny(const void* a, long long lda, const void* w, long long ldw, void* out, long long ldo,
-                                  int M, int N, int K, int splits, int out_f32, int* status, cudaStream_t stream) {
+                                  int M, int N, int K, int splits, int out_f32, int swiglu, int* status,
+                                  cudaStream_t stream) {
     if (M <= 0 || N <= 0) return KL_OK;
     if (M > 64) return KL_ERR_BAD_SIZE;
+    if (swiglu && (splits != 1 || out_f32 || N % 128)) return KL_ERR_BAD_SIZE;
     if (!aligned_operand(a, lda, K) || !aligned_operand(w, ldw, K)) return KL_ERR_BAD_ALIGN;
     const int k_blocks = (K + TC_BK - 1) / TC_BK;
     if (splits < 1 || splits > k_blocks || splits > 65535) return KL_ERR_BAD_SIZE;
@@ -419,7 +522,7 @@ KL_API int kl_gemm_tcgen05_skinny(const void* a, long long lda, const void* w, l
     int rc;
     if ((rc = make_map(&ma, w, N, K, ldw, TC_BM)) != KL_OK) return rc;
     if ((rc = make_map(&mb, a, M, K, lda, bn)) != KL_OK) return rc;
-    GemmArgs args{out, ldo, (long long)M * ldo, N, M, k_blocks, out_f32, status};
+    GemmArgs args{out, ldo, (long long)M * ldo, N, M, k_blocks, out_f32, status, 0, 0, swiglu};
     dim3 grid((N + TC_BM - 1) / TC_BM, 1, splits);
     // two CTAs share an SM so that one's epilogue overlaps the other's loads
     if (bn == 16) return launch<16, 6, true>(ma, mb, args, grid, stream);

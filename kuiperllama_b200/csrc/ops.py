@@ -300,16 +300,19 @@ def skinny_splits(N: int, K: int) -> int:
     return (k_blocks + per - 1) // per
 
 
-def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
-    """out[M, N] = a @ w^T on the tensor cores, tokens as tile rows (any M)."""
+def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bool = False) -> None:
+    """out[M, N] = a @ w^T on the tensor cores, tokens as tile rows (any M).  With ``swiglu``
+    the rows of ``w`` alternate 64 gate rows and 64 up rows and out[M, N / 2] receives
+    silu(gate) * up."""
     _cuda(a, w, out)
     (M, K), (N, K2) = a.shape, w.shape
-    _need(K == K2 and out.shape[0] >= M and out.shape[1] == N, "gemm_tcgen05: shapes")
+    _need(K == K2 and out.shape[0] >= M and out.shape[1] == (N // 2 if swiglu else N), "gemm_tcgen05: shapes")
+    _need(not swiglu or (N % 128 == 0 and out.dtype == torch.bfloat16), "gemm_tcgen05: swiglu needs N % 128 == 0 and bf16 out")
     _need(_tc_ok(a, w, out), "gemm_tcgen05: operands must be bfloat16 with 16-byte aligned rows")
     _check(lib("gemm_tcgen05").kl_gemm_tcgen05(_ptr(a), ctypes.c_longlong(a.stride(0)), _ptr(w),
                                                ctypes.c_longlong(w.stride(0)), _ptr(out), ctypes.c_longlong(out.stride(0)),
-                                               M, N, K, int(out.dtype == torch.float32), _ptr(status_word(a.device)),
-                                               _stream()), "gemm_tcgen05")
+                                               M, N, K, int(out.dtype == torch.float32), int(swiglu),
+                                               _ptr(status_word(a.device)), _stream()), "gemm_tcgen05")
 
 
 def gemm_skinny_partials(a: torch.Tensor, w: torch.Tensor, splits: Optional[int] = None) -> Optional[torch.Tensor]:
@@ -328,28 +331,32 @@ def gemm_skinny_partials(a: torch.Tensor, w: torch.Tensor, splits: Optional[int]
     partial = torch.empty((splits, M, N), dtype=torch.float32, device=a.device)
     _check(lib("gemm_tcgen05").kl_gemm_tcgen05_skinny(
         _ptr(a), ctypes.c_longlong(a.stride(0)), _ptr(w), ctypes.c_longlong(w.stride(0)), _ptr(partial),
-        ctypes.c_longlong(N), M, N, K, splits, 1, _ptr(status_word(a.device)), _stream()), "gemm_skinny")
+        ctypes.c_longlong(N), M, N, K, splits, 1, 0, _ptr(status_word(a.device)), _stream()), "gemm_skinny")
     return partial
 
 
-def gemm_skinny(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, splits: Optional[int] = None) -> None:
+def gemm_skinny(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, splits: Optional[int] = None,
+                swiglu: bool = False) -> None:
     """out[M, N] = a @ w^T for M <= 64 tokens: weights as tile rows, each weight read once, the
-    K range cut into ``splits`` pieces whose float32 partial sums are added in a fixed order."""
+    K range cut into ``splits`` pieces whose float32 partial sums are added in a fixed order.
+    With ``swiglu`` (rows of ``w`` alternate 64 gate and 64 up rows; no cut) out[M, N / 2]
+    receives silu(gate) * up."""
     _cuda(a, w, out)
     (M, K), (N, K2) = a.shape, w.shape
-    _need(K == K2 and out.shape[0] >= M and out.shape[1] == N and M <= 64, "gemm_skinny: shapes")
+    _need(K == K2 and out.shape[0] >= M and out.shape[1] == (N // 2 if swiglu else N) and M <= 64, "gemm_skinny: shapes")
     _need(_tc_ok(a, w, out), "gemm_skinny: operands must be bfloat16 with 16-byte aligned rows")
-    splits = skinny_splits(N, K) if splits is None else splits
+    _need(not swiglu or (N % 128 == 0 and out.dtype == torch.bfloat16), "gemm_skinny: swiglu needs N % 128 == 0 and bf16 out")
+    splits = 1 if swiglu else (skinny_splits(N, K) if splits is None else splits)
     L = lib("gemm_tcgen05")
     st = _ptr(status_word(a.device))
     if splits == 1:
         _check(L.kl_gemm_tcgen05_skinny(_ptr(a), ctypes.c_longlong(a.stride(0)), _ptr(w), ctypes.c_longlong(w.stride(0)),
                                         _ptr(out), ctypes.c_longlong(out.stride(0)), M, N, K, 1,
-                                        int(out.dtype == torch.float32), st, _stream()), "gemm_skinny")
+                                        int(out.dtype == torch.float32), int(swiglu), st, _stream()), "gemm_skinny")
         return
     partial = torch.empty((splits, M, N), dtype=torch.float32, device=a.device)
     _check(L.kl_gemm_tcgen05_skinny(_ptr(a), ctypes.c_longlong(a.stride(0)), _ptr(w), ctypes.c_longlong(w.stride(0)),
-                                    _ptr(partial), ctypes.c_longlong(N), M, N, K, splits, 1, st, _stream()), "gemm_skinny")
+                                    _ptr(partial), ctypes.c_longlong(N), M, N, K, splits, 1, 0, st, _stream()), "gemm_skinny")
     _check(L.kl_splitk_reduce(_ptr(partial), splits, M, N, _ptr(out), ctypes.c_longlong(out.stride(0)),
                               int(out.dtype == torch.float32), _stream()), "splitk_reduce")
 
@@ -433,6 +440,27 @@ def attention_mma(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache: to
         _ptr(cu_tokens), _ptr(seq_slots), _ptr(seq_starts), _ptr(seq_new), _ptr(po), _ptr(pml), n_seqs, max_new, n_rows,
         num_heads, num_kv_heads, head_dim, ctypes.c_float(scale), int(window or 0), splits, int(few_rows), _stream()),
         "attention_mma", 2 if splits > 1 else 1)
+
+
+def swiglu_fusable(hidden: int, inter: int, dtype: torch.dtype) -> bool:
+    """Whether gate and up can be one product whose epilogue applies silu(gate) * up: bfloat16,
+    rows on 16-byte boundaries, and an intermediate size that is a multiple of 64 (the weights
+    are then stored as alternating blocks of 64 gate rows and 64 up rows)."""
+    return dtype == torch.bfloat16 and inter % 64 == 0 and hidden % 8 == 0
+
+
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """[I, K] and [I, K] -> [2 I, K]: 64 gate rows, the 64 up rows of the same features, and so on."""
+    inter, k = gate.shape
+    return torch.stack([gate.view(inter // 64, 64, k), up.view(inter // 64, 64, k)], dim=1).reshape(2 * inter, k).contiguous()
+
+
+def matmul_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out[M, I] = silu(a @ gate^T) * (a @ up^T) in one kernel; ``w_gate_up`` from ``interleave_gate_up``."""
+    if a.shape[0] <= 64:
+        gemm_skinny(a, w_gate_up, out, swiglu=True)
+    else:
+        gemm_tcgen05(a, w_gate_up, out, swiglu=True)
 
 
 # Which kernel decode steps of the bfloat16 path use when both fit: "mma" (tensor cores) or

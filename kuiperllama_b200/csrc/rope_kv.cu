@@ -58,6 +58,42 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const float* __restric
     // items, first the (head, j) pairs of queries and keys (element j and element j + hd/2 are
     // handled together, so each thread owns what it reads and writes), then the value elements.
     const int n_qk = (H + KV) * half;
+    if constexpr (sizeof(T) == 2) {
+        if (rot == hd && prow == nullptr && (half & 7) == 0) {
+            // bfloat16 rows without partial sums (prefill): eight pairs per thread, 16-byte accesses
+            const int h8 = half >> 3;                       // groups of eight pairs per head
+            const int n_qk8 = (H + KV) * h8;
+            const int total = n_qk8 + (write_kv ? KV * hd / 8 : 0);
+            for (int w = blockIdx.y * blockDim.x + threadIdx.x; w < total; w += gridDim.y * blockDim.x) {
+                if (w < n_qk8) {
+                    const int head = w / h8, j0 = (w - head * h8) << 3;
+                    if (head >= H && !write_kv) continue;
+                    T* h = row + (size_t)head * hd;
+                    uint4 ra = *reinterpret_cast<const uint4*>(h + j0), rb = *reinterpret_cast<const uint4*>(h + j0 + half);
+                    __nv_bfloat162* pa = reinterpret_cast<__nv_bfloat162*>(&ra);
+                    __nv_bfloat162* pb = reinterpret_cast<__nv_bfloat162*>(&rb);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float2 a = __bfloat1622float2(pa[e]), b = __bfloat1622float2(pb[e]);
+                        float s0, c0, s1, c1;
+                        sincosf((float)pos * inv_freq[j0 + 2 * e], &s0, &c0);
+                        sincosf((float)pos * inv_freq[j0 + 2 * e + 1], &s1, &c1);
+                        pa[e] = __floats2bfloat162_rn(a.x * c0 - b.x * s0, a.y * c1 - b.y * s1);
+                        pb[e] = __floats2bfloat162_rn(b.x * c0 + a.x * s0, b.y * c1 + a.y * s1);
+                    }
+                    T* dst = head < H ? h : (T*)k_cache + cache_row_offset(block_table, blocks_per_seq, slot, pos, head - H, KV, hd);
+                    *reinterpret_cast<uint4*>(dst + j0) = ra;
+                    *reinterpret_cast<uint4*>(dst + j0 + half) = rb;
+                } else {
+                    const int idx = (w - n_qk8) << 3;
+                    const int g = idx / hd, e = idx - g * hd;
+                    T* dst = (T*)v_cache + cache_row_offset(block_table, blocks_per_seq, slot, pos, g, KV, hd);
+                    *reinterpret_cast<uint4*>(dst + e) = *reinterpret_cast<const uint4*>(row + (size_t)(H + KV) * hd + idx);
+                }
+            }
+            return;
+        }
+    }
     if (rot == hd) {
         const int total = n_qk + (write_kv ? KV * hd : 0);
         for (int w = blockIdx.y * blockDim.x + threadIdx.x; w < total; w += gridDim.y * blockDim.x) {
@@ -134,8 +170,12 @@ KL_API int kl_rope_kv_write(void* qkv, const float* partials, int n_partials, lo
     if (n_partials < 0 || (n_partials > 0 && partials == nullptr)) return KL_ERR_BAD_SIZE;
     const int work = (H + KV) * hd / 2 + (write_kv ? KV * hd : 0);
     const int threads = work >= 1024 ? 256 : (work >= 256 ? 128 : 64);
-    // full rotation: a token's work is spread over several CTAs (one item per thread)
-    const int ctas = rotary_dim == hd ? (work + threads - 1) / threads : 1;
+    // full rotation: a token's work is spread over several CTAs (one item per thread; rows of
+    // bfloat16 without partial sums take eight items per thread)
+    const bool vec = dtype == KL_BF16 && n_partials == 0 && rotary_dim == hd && (hd % 16) == 0 &&
+                     (((H + 2 * KV) * hd) % 8) == 0 && ((uintptr_t)qkv & 15) == 0;
+    const int items = vec ? (work + 7) / 8 : work;
+    const int ctas = rotary_dim == hd ? (items + threads - 1) / threads : 1;
     if (dtype == KL_F32)
         rope_kv_write_kernel<float><<<dim3(n_tokens, ctas), threads, 0, stream>>>((float*)qkv, partials, n_partials,
             (size_t)partial_stride, inv_freq, rotary_dim, positions,

@@ -17,7 +17,8 @@ class SwiGLUFeedForward(FeedForward):
     """f = W_down (silu(W_gate n) * W_up n), silu(g) = g / (1 + exp(-g)), no bias
     (ExiledOfCode/KuiperLLama kuiper/source/model/llama3.cpp:692-718, swiglu_kernel.cu:18-21;
     gate = w1, up = w3, down = w2, tools/export_llama3.py:583-585).  Gate and up are stacked
-    into one matrix at load.  Spec: ``hidden_size``, ``intermediate_size``, ``names``."""
+    into one matrix at load (and the activation is applied in that product's epilogue where the
+    tensor-core kernel runs).  Spec: ``hidden_size``, ``intermediate_size``, ``names``."""
 
     @classmethod
     def manifest(cls, spec: PartSpec, prefix: str) -> Dict[str, TensorDecl]:
@@ -30,12 +31,18 @@ class SwiGLUFeedForward(FeedForward):
         self.hidden, self.inter = int(spec["hidden_size"]), int(spec["intermediate_size"])
         n = spec["names"]
         dev, dt = runtime.device, runtime.dtype
-        stacked = torch.cat([tensors[prefix + n[k]].to(device=dev, dtype=dt) for k in ("gate", "up")], dim=0)
-        self.gate_up = Linear(stacked, runtime)
+        gate, up = (tensors[prefix + n[k]].to(device=dev, dtype=dt) for k in ("gate", "up"))
+        # One product for gate and up.  Where the tensor-core kernel can apply the activation in
+        # its epilogue, the rows are stored as alternating blocks of 64 gate and 64 up rows.
+        self.fused = ops.swiglu_fusable(self.hidden, self.inter, dt)
+        self.gate_up = Linear(ops.interleave_gate_up(gate, up) if self.fused else torch.cat([gate, up], dim=0), runtime)
+        del gate, up
         self.down = Linear(tensors[prefix + n["down"]], runtime)
 
     def forward(self, x: torch.Tensor, step: StepContext) -> torch.Tensor:
-        gu = self.gate_up.forward(x)
         act = torch.empty((x.shape[0], self.inter), dtype=self.runtime.dtype, device=x.device)
-        ops.swiglu(gu, act)
+        if self.fused:
+            ops.matmul_swiglu(x, self.gate_up.weight, act)
+        else:
+            ops.swiglu(self.gate_up.forward(x), act)
         return self.down.forward(act, allow_partials=True)

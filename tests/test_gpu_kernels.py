@@ -529,3 +529,23 @@ def test_attention_mma_finds_one_far_key_among_thousands(ops, few_rows, splits):
         for j in range(new):
             if far <= n - new + j:
                 _close(out[j].view(H, hd), want, "bfloat16", f"far key at {far}, query {j}")
+
+
+@pytest.mark.parametrize("M,I,K", [(1, 64, 64), (8, 512, 192), (33, 14336 // 8, 4096 // 8), (64, 128, 72), (65, 512, 192),
+                                   (300, 1792, 520), (2048, 256, 4096)])
+def test_gate_up_product_with_swiglu_epilogue(ops, M, I, K):
+    torch.manual_seed(18)
+    x = torch.randn(M, K, device=DEV).bfloat16()
+    gate = (torch.randn(I, K, device=DEV) * 0.05).bfloat16()
+    up = (torch.randn(I, K, device=DEV) * 0.05).bfloat16()
+    assert ops.swiglu_fusable(K, I, torch.bfloat16)
+    w = ops.interleave_gate_up(gate, up)
+    assert torch.equal(w[64:128], up[:64]) and torch.equal(w[128:192], gate[64:128]) if I > 64 else True
+    out = torch.full((M, I), 7.0, device=DEV, dtype=torch.bfloat16)
+    ops.matmul_swiglu(x, w, out)
+    ops.check_status(out.device)
+    g = x.double().cpu() @ gate.double().cpu().T
+    u = x.double().cpu() @ up.double().cpu().T
+    ref = g / (1 + torch.exp(-g)) * u
+    err = float((out.double().cpu() - ref).abs().max())
+    assert err <= 8e-3 * float(ref.abs().max()) + 1e-6, f"fused swiglu {M}x{I}x{K}: error {err:.3e}"
