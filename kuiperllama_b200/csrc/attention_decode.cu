@@ -45,6 +45,8 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
                         const int* __restrict__ positions, const int* __restrict__ token_slot,
                         float* __restrict__ partial_o, float* __restrict__ partial_ml,
                         int H, int KV, float scale, int window) {
+    pdl_launch_dependents();
+    pdl_wait();
     constexpr int DPL = HD / LPK;                 // dimensions per lane
     constexpr int KPW = 32 / LPK;                 // lane groups (keys in flight) per warp
     static_assert(DPL == 8, "a lane holds 8 dimensions: one 16-byte load per key");
@@ -191,6 +193,8 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
 template <int HD>
 __global__ void decode_combine_kernel(const float* __restrict__ partial_o, const float* __restrict__ partial_ml,
                                       const int* __restrict__ token_slot, bf16* __restrict__ out, int H, int S) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int row = blockIdx.x, h = blockIdx.y;
     if (token_slot[row] < 0) return;
     const size_t base = ((size_t)row * H + h) * S;
@@ -218,7 +222,7 @@ static int launch_decode(const bf16* q, int q_stride, bf16* out, const bf16* k, 
     const dim3 grid(rows, KV * tiles, S);
     if (grid.y > 65535 || grid.z > 65535) return KL_ERR_BAD_SIZE;
 #define KL_DA_LAUNCH(GT)                                                                                              \
-    decode_attention_kernel<HD, LPK, GT><<<grid, DA_WARPS * 32, 0, stream>>>(q, q_stride, out, k, v, table, bps,        \
+    launch_kernel(decode_attention_kernel<HD, LPK, GT>, grid, DA_WARPS * 32, 0, stream, q, q_stride, out, k, v, table, bps,        \
         positions, token_slot, po, pml, H, KV, scale, window)
     if (gt == 1) KL_DA_LAUNCH(1);
     else if (gt == 2) KL_DA_LAUNCH(2);
@@ -226,7 +230,7 @@ static int launch_decode(const bf16* q, int q_stride, bf16* out, const bf16* k, 
 #undef KL_DA_LAUNCH
     KL_LAUNCH_CHECK();
     if (S > 1) {
-        decode_combine_kernel<HD><<<dim3(rows, H), HD < 128 ? 32 : 128, 0, stream>>>(po, pml, token_slot, out, H, S);
+        launch_kernel(decode_combine_kernel<HD>, dim3(rows, H), HD < 128 ? 32 : 128, 0, stream, po, pml, token_slot, out, H, S);
         KL_LAUNCH_CHECK();
     }
     return KL_OK;

@@ -67,6 +67,8 @@ attention_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict_
                      const int* __restrict__ seq_starts, const int* __restrict__ seq_new,
                      float* __restrict__ part_o, float* __restrict__ part_ml,
                      int H, int KV, int Gp, float scale_log2, int window, int S) {
+    pdl_launch_dependents();
+    pdl_wait();
     constexpr int THREADS = 32 * WM * WN;
     constexpr int ROWS = 16 * WM;
     constexpr int KPW = PAGE / WN;                       // keys of a page that one warp handles
@@ -290,6 +292,8 @@ attention_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict_
 template <int HD>
 __global__ void attention_mma_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                              bf16* __restrict__ out, int H, int S) {
+    pdl_launch_dependents();
+    pdl_wait();
     const size_t orow = (size_t)blockIdx.x * H + blockIdx.y;
     float M = -INFINITY;
     for (int z = 0; z < S; ++z) M = fmaxf(M, part_ml[(orow * S + z) * 2]);
@@ -325,11 +329,11 @@ static int launch_mma(const bf16* q, int q_stride, bf16* out, const bf16* k, con
         KL_CUDA(cudaFuncSetAttribute(attention_mma_kernel<HD, WM, WN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         configured = true;
     }
-    attention_mma_kernel<HD, WM, WN><<<grid, 32 * WM * WN, smem, stream>>>(q, q_stride, out, k, v, table, bps, cu, slots,
+    launch_kernel(attention_mma_kernel<HD, WM, WN>, grid, 32 * WM * WN, smem, stream, q, q_stride, out, k, v, table, bps, cu, slots,
         starts, news, po, pml, H, KV, Gp, scale * 1.4426950408889634f, window, S);
     KL_LAUNCH_CHECK();
     if (S > 1) {
-        attention_mma_combine_kernel<HD><<<dim3(n_rows, H), HD <= 64 ? 32 : 64, 0, stream>>>(po, pml, out, H, S);
+        launch_kernel(attention_mma_combine_kernel<HD>, dim3(n_rows, H), HD <= 64 ? 32 : 64, 0, stream, po, pml, out, H, S);
         KL_LAUNCH_CHECK();
     }
     return KL_OK;

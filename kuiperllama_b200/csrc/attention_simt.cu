@@ -53,6 +53,8 @@ attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out
                       const int* __restrict__ block_table, int blocks_per_seq,
                       const int* __restrict__ positions, const int* __restrict__ token_slot,
                       int H, int KV, int hd, float scale, int window) {
+    pdl_launch_dependents();
+    pdl_wait();
     extern __shared__ float smem[];
     float* q_s = smem;                               // [hd]
     float* m_s = q_s + hd;                           // [ATT_WARPS]
@@ -145,11 +147,11 @@ KL_API int kl_attention_simt(const void* q, int q_stride, void* out, const void*
     const dim3 grid(n_tokens, H);
     const size_t smem = (size_t)(hd + 2 * ATT_WARPS + ATT_WARPS * hd) * sizeof(float);
     if (dtype == KL_F32)
-        attention_simt_kernel<float><<<grid, ATT_WARPS * 32, smem, stream>>>((const float*)q, q_stride, (float*)out,
+        launch_kernel(attention_simt_kernel<float>, grid, ATT_WARPS * 32, smem, stream, (const float*)q, q_stride, (float*)out,
             (const float*)k_cache, (const float*)v_cache, block_table, blocks_per_seq, positions, token_slot, H, KV,
             hd, scale, window);
     else if (dtype == KL_BF16)
-        attention_simt_kernel<bf16><<<grid, ATT_WARPS * 32, smem, stream>>>((const bf16*)q, q_stride, (bf16*)out,
+        launch_kernel(attention_simt_kernel<bf16>, grid, ATT_WARPS * 32, smem, stream, (const bf16*)q, q_stride, (bf16*)out,
             (const bf16*)k_cache, (const bf16*)v_cache, block_table, blocks_per_seq, positions, token_slot, H, KV,
             hd, scale, window);
     else

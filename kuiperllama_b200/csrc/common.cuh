@@ -7,6 +7,8 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
 
 #define KL_API extern "C" __attribute__((visibility("default")))
 
@@ -38,6 +40,42 @@ enum : int { KL_F32 = 0, KL_BF16 = 1 };
 namespace kl {
 
 typedef __nv_bfloat16 bf16;
+
+// Programmatic dependent launch.  Every kernel of this package is launched with the
+// programmatic-stream-serialization attribute (unless KL_PDL=0 is in the environment): it may
+// start while the kernel before it in the stream is still running.  A kernel therefore calls
+// pdl_wait() before it reads anything another kernel wrote or writes anything at all; what it
+// does before that (barrier set-up, tensor-memory allocation, loads of weights, which no
+// kernel writes) overlaps the tail of its predecessor.  pdl_launch_dependents() at the top
+// lets the next kernel in the stream do the same with this one.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+inline bool pdl_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("KL_PDL");
+        v = (e != nullptr && e[0] == '0') ? 0 : 1;
+    }
+    return v != 0;
+}
+
+// Launch on `stream`; a failure is left for cudaGetLastError (KL_LAUNCH_CHECK).
+template <typename... KArgs, typename... Args>
+inline void launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 
 __device__ __forceinline__ float to_f32(float v) { return v; }
 __device__ __forceinline__ float to_f32(bf16 v) { return __bfloat162float(v); }

@@ -18,6 +18,8 @@ template <typename TI, typename TO>
 __global__ void __launch_bounds__(GS_THREADS)
 gemm_simt_kernel(const TI* __restrict__ A, int lda, const TI* __restrict__ W, int ldw, TO* __restrict__ C, int ldc,
                  int M, int N, int K) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float As[GS_BK][GS_BM + 4];
     __shared__ float Ws[GS_BK][GS_BN + 4];
     const int m0 = blockIdx.y * GS_BM, n0 = blockIdx.x * GS_BN;
@@ -78,13 +80,13 @@ KL_API int kl_gemm_simt(const void* A, int lda, const void* W, int ldw, void* C,
     const dim3 grid((N + GS_BN - 1) / GS_BN, (M + GS_BM - 1) / GS_BM);
     if (grid.y > 65535) return KL_ERR_BAD_SIZE;
     if (in_dtype == KL_F32 && out_dtype == KL_F32)
-        gemm_simt_kernel<float, float><<<grid, GS_THREADS, 0, stream>>>((const float*)A, lda, (const float*)W, ldw,
+        launch_kernel(gemm_simt_kernel<float, float>, grid, GS_THREADS, 0, stream, (const float*)A, lda, (const float*)W, ldw,
                                                                         (float*)C, ldc, M, N, K);
     else if (in_dtype == KL_BF16 && out_dtype == KL_BF16)
-        gemm_simt_kernel<bf16, bf16><<<grid, GS_THREADS, 0, stream>>>((const bf16*)A, lda, (const bf16*)W, ldw,
+        launch_kernel(gemm_simt_kernel<bf16, bf16>, grid, GS_THREADS, 0, stream, (const bf16*)A, lda, (const bf16*)W, ldw,
                                                                       (bf16*)C, ldc, M, N, K);
     else if (in_dtype == KL_BF16 && out_dtype == KL_F32)
-        gemm_simt_kernel<bf16, float><<<grid, GS_THREADS, 0, stream>>>((const bf16*)A, lda, (const bf16*)W, ldw,
+        launch_kernel(gemm_simt_kernel<bf16, float>, grid, GS_THREADS, 0, stream, (const bf16*)A, lda, (const bf16*)W, ldw,
                                                                        (float*)C, ldc, M, N, K);
     else
         return KL_ERR_BAD_DTYPE;

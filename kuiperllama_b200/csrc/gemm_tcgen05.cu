@@ -185,6 +185,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const int kb1 = min(args.k_blocks, kb0 + per);
     const int nkb = max(kb1 - kb0, 0);
 
+    pdl_launch_dependents();                    // the next kernel in the stream may set itself up while this one runs
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
         mbar_init(acc_ready, 1);
@@ -202,9 +203,23 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         // ---------------------------------------------------------------- TMA producer
         if (elect_one()) {
             int issued = 0;
-            for (int i = 0; i < nkb; ++i) {
+            // Weights are written by no kernel, so their tiles for the first stages are requested
+            // before this grid waits for the kernel before it; the activations come after.
+            const int pre = min(nkb, STAGES);
+            for (int i = 0; i < pre; ++i) {
+                mbar_expect_tx(&full[i], A_BYTES + B_BYTES);
+                if constexpr (WEIGHT_ROWS) tma_load_2d(tiles_a + i * A_BYTES, &map_a, &full[i], (kb0 + i) * TC_BK, tile_a * TC_BM);
+                else tma_load_2d(tiles_b + i * B_BYTES, &map_b, &full[i], (kb0 + i) * TC_BK, tile_b * BN);
+            }
+            pdl_wait();
+            for (int i = 0; i < pre; ++i) {
+                if constexpr (WEIGHT_ROWS) tma_load_2d(tiles_b + i * B_BYTES, &map_b, &full[i], (kb0 + i) * TC_BK, tile_b * BN);
+                else tma_load_2d(tiles_a + i * A_BYTES, &map_a, &full[i], (kb0 + i) * TC_BK, tile_a * TC_BM);
+                issued = i + 1;
+            }
+            for (int i = pre; i < nkb; ++i) {
                 const int s = i % STAGES;
-                if (i >= STAGES && !mbar_wait(&empty[s], ((i / STAGES) - 1) & 1, abort_flag, args.status, 1)) break;
+                if (!mbar_wait(&empty[s], ((i / STAGES) - 1) & 1, abort_flag, args.status, 1)) break;
                 mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
                 tma_load_2d(tiles_a + s * A_BYTES, &map_a, &full[s], (kb0 + i) * TC_BK, tile_a * TC_BM);
                 tma_load_2d(tiles_b + s * B_BYTES, &map_b, &full[s], (kb0 + i) * TC_BK, tile_b * BN);
@@ -238,6 +253,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     } else {
         // ---------------------------------------------------------------- epilogue: warps 2..5
         const int quarter = warp & 3;                         // the 32 tensor-memory lanes this warp may read
+        pdl_wait();                                           // before this grid writes anything
         const bool ok = mbar_wait(acc_ready, 0, abort_flag, args.status, 3) && !*abort_flag;
         tc_fence_after();
         const int row = tile_a * TC_BM + quarter * 32 + lane;              // row of the A operand
@@ -473,7 +489,7 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& 
                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         configured = true;
     }
-    gemm_tcgen05_kernel<BN, STAGES, WEIGHT_ROWS><<<grid, TC_THREADS, smem, stream>>>(ma, mb, args);
+    launch_kernel(gemm_tcgen05_kernel<BN, STAGES, WEIGHT_ROWS>, grid, TC_THREADS, smem, stream, ma, mb, args);
     KL_LAUNCH_CHECK();
     return KL_OK;
 }
@@ -535,6 +551,8 @@ namespace kl {
 template <typename TO>
 __global__ void splitk_reduce_kernel(const float* __restrict__ partial, int splits, int M, int N, TO* __restrict__ out,
                                      long long ldo) {
+    pdl_launch_dependents();
+    pdl_wait();
     const size_t total = (size_t)M * N;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         float acc = 0.f;
@@ -551,8 +569,8 @@ KL_API int kl_splitk_reduce(const float* partial, int splits, int M, int N, void
     const size_t total = (size_t)M * N;
     const int threads = 256;
     const int blocks = (int)((total + threads - 1) / threads < 148 * 8 ? (total + threads - 1) / threads : 148 * 8);
-    if (out_f32) kl::splitk_reduce_kernel<float><<<blocks, threads, 0, stream>>>(partial, splits, M, N, (float*)out, ldo);
-    else kl::splitk_reduce_kernel<kl::bf16><<<blocks, threads, 0, stream>>>(partial, splits, M, N, (kl::bf16*)out, ldo);
+    if (out_f32) launch_kernel(kl::splitk_reduce_kernel<float>, blocks, threads, 0, stream, partial, splits, M, N, (float*)out, ldo);
+    else launch_kernel(kl::splitk_reduce_kernel<kl::bf16>, blocks, threads, 0, stream, partial, splits, M, N, (kl::bf16*)out, ldo);
     KL_LAUNCH_CHECK();
     return KL_OK;
 }

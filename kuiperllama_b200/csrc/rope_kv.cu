@@ -23,6 +23,8 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const float* __restric
                                      const int* __restrict__ block_table, int blocks_per_seq,
                                      T* __restrict__ k_cache, T* __restrict__ v_cache,
                                      int H, int KV, int hd, int write_kv) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x;
     const int slot = token_slot[t];
     if (slot < 0) return;                                   // a padding row
@@ -177,11 +179,11 @@ KL_API int kl_rope_kv_write(void* qkv, const float* partials, int n_partials, lo
     const int items = vec ? (work + 7) / 8 : work;
     const int ctas = rotary_dim == hd ? (items + threads - 1) / threads : 1;
     if (dtype == KL_F32)
-        rope_kv_write_kernel<float><<<dim3(n_tokens, ctas), threads, 0, stream>>>((float*)qkv, partials, n_partials,
+        launch_kernel(rope_kv_write_kernel<float>, dim3(n_tokens, ctas), threads, 0, stream, (float*)qkv, partials, n_partials,
             (size_t)partial_stride, inv_freq, rotary_dim, positions,
             token_slot, block_table, blocks_per_seq, (float*)k_cache, (float*)v_cache, H, KV, hd, write_kv);
     else if (dtype == KL_BF16)
-        rope_kv_write_kernel<bf16><<<dim3(n_tokens, ctas), threads, 0, stream>>>((bf16*)qkv, partials, n_partials,
+        launch_kernel(rope_kv_write_kernel<bf16>, dim3(n_tokens, ctas), threads, 0, stream, (bf16*)qkv, partials, n_partials,
             (size_t)partial_stride, inv_freq, rotary_dim, positions,
             token_slot, block_table, blocks_per_seq, (bf16*)k_cache, (bf16*)v_cache, H, KV, hd, write_kv);
     else

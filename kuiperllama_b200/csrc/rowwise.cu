@@ -16,6 +16,8 @@ namespace kl {
 template <typename T>
 __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restrict__ table, float* __restrict__ out,
                                  int hidden, int vocab, int* __restrict__ error_flag) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x;
     const int id = ids[t];
     float* o = out + (size_t)t * hidden;
@@ -63,6 +65,8 @@ __global__ void __launch_bounds__(THREADS)
 add_rmsnorm_kernel(float* __restrict__ residual, const T* __restrict__ delta, const float* __restrict__ partials,
                    int n_partials, size_t partial_stride, const float* __restrict__ weight, T* __restrict__ out,
                    const int* __restrict__ rows, int hidden, float eps) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float scratch[33];
     const int r = blockIdx.x;
     const int s = rows ? rows[r] : r;
@@ -145,6 +149,8 @@ add_rmsnorm_kernel(float* __restrict__ residual, const T* __restrict__ delta, co
 // out[t, i] = silu(gu[t, i]) * gu[t, inter + i]; gu is [tokens, 2 * inter] (gate columns first).
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int tokens, int inter) {
+    pdl_launch_dependents();
+    pdl_wait();
     const size_t n = (size_t)tokens * inter;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (size_t)gridDim.x * blockDim.x) {
         const size_t t = idx / inter;
@@ -164,9 +170,9 @@ KL_API int kl_embedding(const int* ids, int n_tokens, const void* table, int tab
     if (n_tokens <= 0) return KL_OK;
     const int threads = hidden >= 1024 ? 256 : 128;
     if (table_dtype == KL_F32)
-        embedding_kernel<float><<<n_tokens, threads, 0, stream>>>(ids, (const float*)table, out, hidden, vocab, error_flag);
+        launch_kernel(embedding_kernel<float>, n_tokens, threads, 0, stream, ids, (const float*)table, out, hidden, vocab, error_flag);
     else if (table_dtype == KL_BF16)
-        embedding_kernel<bf16><<<n_tokens, threads, 0, stream>>>(ids, (const bf16*)table, out, hidden, vocab, error_flag);
+        launch_kernel(embedding_kernel<bf16>, n_tokens, threads, 0, stream, ids, (const bf16*)table, out, hidden, vocab, error_flag);
     else
         return KL_ERR_BAD_DTYPE;
     KL_LAUNCH_CHECK();
@@ -183,7 +189,7 @@ KL_API int kl_add_rmsnorm(float* residual, const void* delta, const float* parti
     // few rows: more threads per row, so that a step of a handful of tokens is not one slow CTA each
     const bool wide = n_rows <= 256 && hidden >= 2048;
 #define KL_NORM(T, THREADS)                                                                                          \
-    add_rmsnorm_kernel<T, THREADS, 8><<<n_rows, THREADS, 0, stream>>>(residual, (const T*)delta, partials, n_partials, \
+    launch_kernel(add_rmsnorm_kernel<T, THREADS, 8>, n_rows, THREADS, 0, stream, residual, (const T*)delta, partials, n_partials, \
         (size_t)partial_stride, weight, (T*)out, rows, hidden, eps)
     if (dtype == KL_F32) { if (wide) KL_NORM(float, 1024); else KL_NORM(float, 256); }
     else if (dtype == KL_BF16) { if (wide) KL_NORM(bf16, 1024); else KL_NORM(bf16, 256); }
@@ -199,9 +205,9 @@ KL_API int kl_swiglu(const void* gate_up, void* out, int tokens, int inter, int 
     const int threads = 256;
     const int blocks = (int)((n + threads - 1) / threads < 148 * 16 ? (n + threads - 1) / threads : 148 * 16);
     if (dtype == KL_F32)
-        swiglu_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, tokens, inter);
+        launch_kernel(swiglu_kernel<float>, blocks, threads, 0, stream, (const float*)gate_up, (float*)out, tokens, inter);
     else if (dtype == KL_BF16)
-        swiglu_kernel<bf16><<<blocks, threads, 0, stream>>>((const bf16*)gate_up, (bf16*)out, tokens, inter);
+        launch_kernel(swiglu_kernel<bf16>, blocks, threads, 0, stream, (const bf16*)gate_up, (bf16*)out, tokens, inter);
     else
         return KL_ERR_BAD_DTYPE;
     KL_LAUNCH_CHECK();

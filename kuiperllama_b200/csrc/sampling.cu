@@ -20,6 +20,8 @@ __device__ __forceinline__ unsigned int ordered_key(float v) {
 
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 argmax_rows_kernel(const float* __restrict__ logits, size_t row_stride, int vocab, int* __restrict__ out) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float sv[32];
     __shared__ int si[32];
     const float* x = logits + (size_t)blockIdx.x * row_stride;
@@ -60,6 +62,8 @@ constexpr int ARGMAX_CHUNK = 4096;
 __global__ void __launch_bounds__(256)
 argmax_chunks_kernel(const float* __restrict__ logits, size_t row_stride, int vocab, float* __restrict__ best_v,
                      int* __restrict__ best_i) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float sv[8];
     __shared__ int si[8];
     const int row = blockIdx.y, chunk = blockIdx.x;
@@ -90,6 +94,8 @@ argmax_chunks_kernel(const float* __restrict__ logits, size_t row_stride, int vo
 
 __global__ void argmax_pick_kernel(const float* __restrict__ best_v, const int* __restrict__ best_i, int chunks,
                                    int* __restrict__ out) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int row = blockIdx.x;
     float best = -INFINITY;
     int bi = 0x7fffffff;
@@ -139,6 +145,8 @@ __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_rows_kernel(const float* __restrict__ logits, size_t row_stride, int vocab, float temperature, int top_k,
                    unsigned long long seed, const int* __restrict__ request_ids, const int* __restrict__ steps,
                    int* __restrict__ out) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float fscratch[33];
     __shared__ int iscratch[33];
     __shared__ double part[SAMPLE_THREADS];
@@ -223,14 +231,14 @@ KL_API int kl_argmax_rows(const float* logits, long long row_stride, int rows, i
     if (rows <= 0) return KL_OK;
     if (vocab <= 0) return KL_ERR_BAD_SIZE;
     if (scratch_v == nullptr || scratch_i == nullptr || rows > 65535) {
-        argmax_rows_kernel<<<rows, SAMPLE_THREADS, 0, stream>>>(logits, (size_t)row_stride, vocab, out);
+        launch_kernel(argmax_rows_kernel, rows, SAMPLE_THREADS, 0, stream, logits, (size_t)row_stride, vocab, out);
         KL_LAUNCH_CHECK();
         return KL_OK;
     }
     const int chunks = (vocab + ARGMAX_CHUNK - 1) / ARGMAX_CHUNK;
-    argmax_chunks_kernel<<<dim3(chunks, rows), 256, 0, stream>>>(logits, (size_t)row_stride, vocab, scratch_v, scratch_i);
+    launch_kernel(argmax_chunks_kernel, dim3(chunks, rows), 256, 0, stream, logits, (size_t)row_stride, vocab, scratch_v, scratch_i);
     KL_LAUNCH_CHECK();
-    argmax_pick_kernel<<<rows, 32, 0, stream>>>(scratch_v, scratch_i, chunks, out);
+    launch_kernel(argmax_pick_kernel, rows, 32, 0, stream, scratch_v, scratch_i, chunks, out);
     KL_LAUNCH_CHECK();
     return KL_OK;
 }
@@ -241,7 +249,7 @@ KL_API int kl_sample_rows(const float* logits, long long row_stride, int rows, i
                           cudaStream_t stream) {
     if (rows <= 0) return KL_OK;
     if (vocab <= 0 || !(temperature > 0.f)) return KL_ERR_BAD_SIZE;
-    sample_rows_kernel<<<rows, SAMPLE_THREADS, 0, stream>>>(logits, (size_t)row_stride, vocab, temperature, top_k,
+    launch_kernel(sample_rows_kernel, rows, SAMPLE_THREADS, 0, stream, logits, (size_t)row_stride, vocab, temperature, top_k,
                                                             seed, request_ids, steps, out);
     KL_LAUNCH_CHECK();
     return KL_OK;
