@@ -1,0 +1,121 @@
+"""Time one kernel of the package alone on synthetic operands (CUDA events, median of
+repeats, a buffer larger than L2 written between repeats), and print the achieved rate.
+
+    python -m kuiperllama_b200.csrc.microbench gemm_skinny --m 8 --n 28672 --k 4096 [--swiglu]
+    python -m kuiperllama_b200.csrc.microbench gemm_tcgen05 --m 2048 --n 6144 --k 4096
+    python -m kuiperllama_b200.csrc.microbench attention_prefill --tokens 2048 --heads 32 --kv-heads 8 --head-dim 128
+    python -m kuiperllama_b200.csrc.microbench attention_decode --batch 64 --context 640 --heads 32 --kv-heads 8 --head-dim 128
+
+It is also the small case that profiler captures of single kernels are taken on.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import sys
+
+import torch
+
+from . import ops
+
+DEV = torch.device("cuda:0")
+
+
+def _time(fn, repeats: int, flush: bool = True) -> float:
+    scratch = torch.empty(192 << 20, dtype=torch.uint8, device=DEV) if flush else None
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(repeats):
+        if scratch is not None:
+            scratch.zero_()                                    # evict L2 (126 MB)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b) * 1e-3)
+    times.sort()
+    return times[len(times) // 2]
+
+
+def _paged(n_seqs: int, length: int, kv: int, hd: int):
+    blocks = (length + ops.PAGE - 1) // ops.PAGE
+    pages = n_seqs * blocks
+    table = torch.randperm(pages).view(n_seqs, blocks).to(torch.int32).to(DEV)
+    k = torch.randn(pages, kv, ops.PAGE, hd, device=DEV).bfloat16()
+    v = torch.randn(pages, kv, ops.PAGE, hd, device=DEV).bfloat16()
+    return table, k, v
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(prog="microbench")
+    ap.add_argument("kernel", choices=["gemm_skinny", "gemm_tcgen05", "attention_prefill", "attention_decode"])
+    ap.add_argument("--m", type=int, default=8)
+    ap.add_argument("--n", type=int, default=4096)
+    ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("--swiglu", action="store_true")
+    ap.add_argument("--splits", type=int, default=None)
+    ap.add_argument("--tokens", type=int, default=2048)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=640)
+    ap.add_argument("--heads", type=int, default=32)
+    ap.add_argument("--kv-heads", type=int, default=8)
+    ap.add_argument("--head-dim", type=int, default=128)
+    ap.add_argument("--repeats", type=int, default=20)
+    ap.add_argument("--simt", action="store_true", help="attention_decode: the split-KV SIMT kernel instead of the tensor-core one")
+    args = ap.parse_args(argv)
+    torch.manual_seed(0)
+    out = {"kernel": args.kernel}
+    if args.kernel in ("gemm_skinny", "gemm_tcgen05"):
+        a = torch.randn(args.m, args.k, device=DEV).bfloat16()
+        w = torch.randn(args.n, args.k, device=DEV).bfloat16()
+        c = torch.empty(args.m, args.n // 2 if args.swiglu else args.n, device=DEV, dtype=torch.bfloat16)
+        if args.kernel == "gemm_skinny":
+            fn = lambda: ops.gemm_skinny(a, w, c, args.splits, swiglu=args.swiglu)
+        else:
+            fn = lambda: ops.gemm_tcgen05(a, w, c, swiglu=args.swiglu)
+        t = _time(fn, args.repeats)
+        flops = 2.0 * args.m * args.n * args.k
+        byts = 2.0 * (args.n * args.k + args.m * args.k + c.numel())
+        out.update(m=args.m, n=args.n, k=args.k, swiglu=args.swiglu, us=round(t * 1e6, 2), tflops=round(flops / t / 1e12, 1),
+                   gbs=round(byts / t / 1e9, 1))
+    else:
+        H, KV, hd = args.heads, args.kv_heads, args.head_dim
+        i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+        scale = 1.0 / math.sqrt(hd)
+        if args.kernel == "attention_prefill":
+            T = args.tokens
+            table, k, v = _paged(1, T, KV, hd)
+            q = torch.randn(T, (H + 2 * KV) * hd, device=DEV).bfloat16()
+            o = torch.empty(T, H * hd, device=DEV, dtype=torch.bfloat16)
+            cu, sl, st, nw = i32([0, T]), i32([0]), i32([0]), i32([T])
+            fn = lambda: ops.attention_mma(q, q.shape[1], o, k, v, table, cu, sl, st, nw, 1, T, T, H, KV, hd, scale, 0, 1, False)
+            t = _time(fn, args.repeats)
+            flops = 4.0 * H * hd * T * (T + 1) / 2
+            out.update(tokens=T, heads=H, kv_heads=KV, head_dim=hd, us=round(t * 1e6, 2), tflops=round(flops / t / 1e12, 1))
+        else:
+            B, N = args.batch, args.context
+            table, k, v = _paged(B, N, KV, hd)
+            q = torch.randn(B, (H + 2 * KV) * hd, device=DEV).bfloat16()
+            o = torch.empty(B, H * hd, device=DEV, dtype=torch.bfloat16)
+            pos, slots = i32([N - 1] * B), i32(list(range(B)))
+            cu, st, nw = i32(list(range(B + 1))), i32([N - 1] * B), i32([1] * B)
+            splits = args.splits or max(1, min(16, (2 * ops.SM_COUNT + B * KV - 1) // (B * KV)))
+            if args.simt:
+                fn = lambda: ops.attention_decode(q, q.shape[1], o, k, v, table, pos, slots, B, H, KV, hd, scale, 0, args.splits)
+            else:
+                fn = lambda: ops.attention_mma(q, q.shape[1], o, k, v, table, cu, slots, st, nw, B, 1, B, H, KV, hd, scale, 0, splits, True)
+            t = _time(fn, args.repeats)
+            byts = 2.0 * 2 * B * N * KV * hd
+            out.update(batch=B, context=N, heads=H, kv_heads=KV, head_dim=hd, splits=splits, us=round(t * 1e6, 2),
+                       gbs=round(byts / t / 1e9, 1))
+    ops.check_status(DEV)
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
