@@ -164,21 +164,27 @@ template <int BN, int STAGES, bool WEIGHT_ROWS>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmArgs args) {
     constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2, B_BYTES = BN * TC_BK * 2;
-    constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+    constexpr uint32_t ACC_COLS = BN < 32 ? 32 : BN;      // columns of one accumulator
+    constexpr uint32_t TMEM_COLS = 2 * ACC_COLS;          // two accumulators: one is drained while the other is filled
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);     // swizzled tiles want 1024-byte alignment
     uint8_t* tiles_a = smem;
     uint8_t* tiles_b = smem + STAGES * A_BYTES;
     uint64_t* full = (uint64_t*)(tiles_b + STAGES * B_BYTES);
     uint64_t* empty = full + STAGES;
-    uint64_t* acc_ready = empty + STAGES;
-    uint32_t* tmem_slot = (uint32_t*)(acc_ready + 1);
+    uint64_t* acc_full = empty + STAGES;                  // [2] an accumulator is complete
+    uint64_t* acc_empty = acc_full + 2;                   // [2] an accumulator has been read out
+    uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    int tile_a, tile_b;                                                // tile index along the A / B operand's rows
-    if constexpr (WEIGHT_ROWS) { tile_a = blockIdx.x; tile_b = 0; }
-    else tile_of(blockIdx.x, args.tiles_m, args.tiles_n, tile_a, tile_b);
+    // A CTA takes the tiles blockIdx.x, blockIdx.x + gridDim.x, ... (tokens-as-rows: one CTA per
+    // SM walks many tiles; weights-as-rows: the grid has one CTA per tile).
+    const int n_tiles = WEIGHT_ROWS ? (int)gridDim.x : args.tiles_m * args.tiles_n;
+    auto tile_at = [&](int t, int& ta, int& tb) {
+        if constexpr (WEIGHT_ROWS) { ta = t; tb = 0; }
+        else tile_of(t, args.tiles_m, args.tiles_n, ta, tb);
+    };
     // k range of this CTA (cut over blockIdx.z)
     const int per = (args.k_blocks + gridDim.z - 1) / gridDim.z;
     const int kb0 = blockIdx.z * per;
@@ -188,7 +194,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     pdl_launch_dependents();                    // the next kernel in the stream may set itself up while this one runs
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-        mbar_init(acc_ready, 1);
+        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -202,29 +208,38 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (warp == 0) {
         // ---------------------------------------------------------------- TMA producer
         if (elect_one()) {
-            int issued = 0;
-            // Weights are written by no kernel, so their tiles for the first stages are requested
-            // before this grid waits for the kernel before it; the activations come after.
-            const int pre = min(nkb, STAGES);
-            for (int i = 0; i < pre; ++i) {
-                mbar_expect_tx(&full[i], A_BYTES + B_BYTES);
-                if constexpr (WEIGHT_ROWS) tma_load_2d(tiles_a + i * A_BYTES, &map_a, &full[i], (kb0 + i) * TC_BK, tile_a * TC_BM);
-                else tma_load_2d(tiles_b + i * B_BYTES, &map_b, &full[i], (kb0 + i) * TC_BK, tile_b * BN);
+            int issued = 0;                                   // k blocks requested so far, over all tiles
+            bool ok = true;
+            for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+                int tile_a, tile_b;
+                tile_at(t, tile_a, tile_b);
+                int first = 0;
+                if (issued == 0) {
+                    // Weights are written by no kernel, so their tiles for the first stages are requested
+                    // before this grid waits for the kernel before it; the activations come after.
+                    const int pre = min(nkb, STAGES);
+                    for (int i = 0; i < pre; ++i) {
+                        mbar_expect_tx(&full[i], A_BYTES + B_BYTES);
+                        if constexpr (WEIGHT_ROWS) tma_load_2d(tiles_a + i * A_BYTES, &map_a, &full[i], (kb0 + i) * TC_BK, tile_a * TC_BM);
+                        else tma_load_2d(tiles_b + i * B_BYTES, &map_b, &full[i], (kb0 + i) * TC_BK, tile_b * BN);
+                    }
+                    pdl_wait();
+                    for (int i = 0; i < pre; ++i) {
+                        if constexpr (WEIGHT_ROWS) tma_load_2d(tiles_b + i * B_BYTES, &map_b, &full[i], (kb0 + i) * TC_BK, tile_b * BN);
+                        else tma_load_2d(tiles_a + i * A_BYTES, &map_a, &full[i], (kb0 + i) * TC_BK, tile_a * TC_BM);
+                    }
+                    issued = first = pre;
+                }
+                for (int i = first; i < nkb; ++i) {
+                    const int s = issued % STAGES;
+                    if (issued >= STAGES && !mbar_wait(&empty[s], ((issued / STAGES) - 1) & 1, abort_flag, args.status, 1)) { ok = false; break; }
+                    mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
+                    tma_load_2d(tiles_a + s * A_BYTES, &map_a, &full[s], (kb0 + i) * TC_BK, tile_a * TC_BM);
+                    tma_load_2d(tiles_b + s * B_BYTES, &map_b, &full[s], (kb0 + i) * TC_BK, tile_b * BN);
+                    ++issued;
+                }
             }
-            pdl_wait();
-            for (int i = 0; i < pre; ++i) {
-                if constexpr (WEIGHT_ROWS) tma_load_2d(tiles_b + i * B_BYTES, &map_b, &full[i], (kb0 + i) * TC_BK, tile_b * BN);
-                else tma_load_2d(tiles_a + i * A_BYTES, &map_a, &full[i], (kb0 + i) * TC_BK, tile_a * TC_BM);
-                issued = i + 1;
-            }
-            for (int i = pre; i < nkb; ++i) {
-                const int s = i % STAGES;
-                if (!mbar_wait(&empty[s], ((i / STAGES) - 1) & 1, abort_flag, args.status, 1)) break;
-                mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
-                tma_load_2d(tiles_a + s * A_BYTES, &map_a, &full[s], (kb0 + i) * TC_BK, tile_a * TC_BM);
-                tma_load_2d(tiles_b + s * B_BYTES, &map_b, &full[s], (kb0 + i) * TC_BK, tile_b * BN);
-                issued = i + 1;
-            }
+            if (issued == 0) pdl_wait();
             if (*abort_flag) {
                 // Wait (bounded) for this CTA's own copies in flight before shared memory goes away.
                 for (int i = max(0, issued - STAGES); i < issued; ++i)
@@ -236,28 +251,44 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         if (elect_one()) {
             constexpr uint32_t idesc = umma_idesc(BN);
             bool ok = true;
-            for (int i = 0; i < nkb && ok; ++i) {
-                const int s = i % STAGES;
-                ok = mbar_wait(&full[s], (i / STAGES) & 1, abort_flag, args.status, 2);
-                if (!ok) break;
-                tc_fence_after();
-                const uint64_t da = smem_desc_sw128(smem_u32(tiles_a + s * A_BYTES));
-                const uint64_t db = smem_desc_sw128(smem_u32(tiles_b + s * B_BYTES));
+            int it = 0, lt = 0;                               // k blocks consumed, tiles done (both over all tiles)
+            for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++lt) {
+                const int buf = lt & 1, use = lt >> 1;
+                if (use > 0) {                                // the epilogue must have read this accumulator out
+                    ok = mbar_wait(&acc_empty[buf], (use - 1) & 1, abort_flag, args.status, 4);
+                    if (!ok) break;
+                    tc_fence_after();
+                }
+                const uint32_t tmem_acc = tmem_base + buf * ACC_COLS;
+                for (int i = 0; i < nkb; ++i, ++it) {
+                    const int s = it % STAGES;
+                    ok = mbar_wait(&full[s], (it / STAGES) & 1, abort_flag, args.status, 2);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint64_t da = smem_desc_sw128(smem_u32(tiles_a + s * A_BYTES));
+                    const uint64_t db = smem_desc_sw128(smem_u32(tiles_b + s * B_BYTES));
 #pragma unroll
-                for (int k = 0; k < TC_BK / 16; ++k)          // 16 bf16 = 32 bytes along the swizzled row: +2 in 16-byte units
-                    umma_bf16(tmem_base, da + 2 * k, db + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
-                umma_commit(&empty[s]);                       // the stage is free once these MMAs have read it
+                    for (int k = 0; k < TC_BK / 16; ++k)      // 16 bf16 = 32 bytes along the swizzled row: +2 in 16-byte units
+                        umma_bf16(tmem_acc, da + 2 * k, db + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+                    umma_commit(&empty[s]);                   // the stage is free once these MMAs have read it
+                }
+                if (!ok) break;
+                umma_commit(&acc_full[buf]);                  // arrives when every MMA above is done (or at once if none)
             }
-            umma_commit(acc_ready);                           // arrives when every MMA above is done (or at once if none)
         }
     } else {
         // ---------------------------------------------------------------- epilogue: warps 2..5
         const int quarter = warp & 3;                         // the 32 tensor-memory lanes this warp may read
         pdl_wait();                                           // before this grid writes anything
-        const bool ok = mbar_wait(acc_ready, 0, abort_flag, args.status, 3) && !*abort_flag;
+        int lt = 0;
+        for (int t = blockIdx.x; t < n_tiles; t += gridDim.x, ++lt) {
+        int tile_a, tile_b;
+        tile_at(t, tile_a, tile_b);
+        const int buf = lt & 1;
+        const bool ok = mbar_wait(&acc_full[buf], (lt >> 1) & 1, abort_flag, args.status, 3) && !*abort_flag;
         tc_fence_after();
         const int row = tile_a * TC_BM + quarter * 32 + lane;              // row of the A operand
-        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        const uint32_t taddr = tmem_base + buf * ACC_COLS + ((uint32_t)(quarter * 32) << 16);
         if constexpr (WEIGHT_ROWS) {
             if (args.swiglu) {
                 // Tile rows 0..63 are gate features, 64..127 the up rows of the same features.  The
@@ -408,6 +439,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 }
             }
         }
+        // this accumulator may be filled again once all four warps have read it out
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[buf]);
+        if (!ok) break;
+        }
     }
     tc_fence_before();
     __syncthreads();
@@ -482,7 +519,7 @@ static int make_map(CUtensorMap* out, const void* ptr, int rows, int cols, long 
 
 template <int BN, int STAGES, bool WEIGHT_ROWS>
 static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& args, dim3 grid, cudaStream_t stream) {
-    constexpr size_t smem = (size_t)STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + (2 * STAGES + 1) * 8 + 16 + 1024;
+    constexpr size_t smem = (size_t)STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + (2 * STAGES + 4) * 8 + 16 + 1024;
     static bool configured = false;
     if (!configured) {
         KL_CUDA(cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, STAGES, WEIGHT_ROWS>,
@@ -516,7 +553,13 @@ KL_API int kl_gemm_tcgen05(const void* a, long long lda, const void* w, long lon
     const int tiles_m = (M + TC_BM - 1) / TC_BM, tiles_n = (N + 255) / 256;
     GemmArgs args{out, ldo, 0, M, N, (K + TC_BK - 1) / TC_BK, out_f32, status, tiles_m, tiles_n, swiglu};
     if ((long long)tiles_m * tiles_n > 0x7fffffffLL) return KL_ERR_BAD_SIZE;
-    dim3 grid(tiles_m * tiles_n, 1, 1);
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0;
+        KL_CUDA(cudaGetDevice(&dev));
+        KL_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    }
+    dim3 grid(min(tiles_m * tiles_n, sms), 1, 1);      // one CTA per SM walks the tiles
     return launch<256, 4, false>(ma, mb, args, grid, stream);
 }
 
