@@ -59,7 +59,7 @@ __device__ __forceinline__ void load_page(bf16* stage, const bf16* __restrict__ 
 }
 
 template <int HD, int WM, int WN>
-__global__ void __launch_bounds__(32 * WM * WN)
+__global__ void __launch_bounds__(32 * WM * WN, 3)        // three CTAs per SM: 168 registers, 3 x 64 KB of stages
 attention_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out,
                      const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                      const int* __restrict__ block_table, int blocks_per_seq,
@@ -84,7 +84,9 @@ attention_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict_
     const int G = H / KV;
     const int BT = ROWS / Gp;                            // tokens per CTA
     const int T = seq_new[b];
-    const int t0 = blockIdx.x * BT;
+    // Tiles late in a sequence read the most keys: they are started first (CTAs are handed out
+    // in ascending blockIdx.x), so the short ones fill the machine's tail.
+    const int t0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * BT;
     if (t0 >= T) return;
     const int start = seq_starts[b], slot = seq_slots[b], row0 = cu_tokens[b];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
