@@ -58,6 +58,22 @@ __device__ __forceinline__ void load_page(bf16* stage, const bf16* __restrict__ 
     }
 }
 
+// What a decode step may fold into the attention kernel (one token per sequence): the sum of
+// the q/k/v product's float32 pieces, the rotation of q and k, the write of the new key and
+// value into the cache (by the CTA whose pages end at the token's position), and the merge of a
+// sequence's splits (by the last of its CTAs to finish; `counters` are zero between launches).
+struct DecodeFuse {
+    int enabled;
+    const float* partials;        // [n_partials][rows][(H + 2 KV) * HD] float32, or null
+    int n_partials;
+    size_t partial_stride;
+    const bf16* qkv;              // [rows][(H + 2 KV) * HD] bfloat16 when there are no partials
+    const float* inv_freq;        // [HD / 2]
+    bf16* k_cache_w;              // the cache, writable
+    bf16* v_cache_w;
+    int* counters;                // [rows * KV], zero
+};
+
 template <int HD, int WM, int WN>
 __global__ void __launch_bounds__(32 * WM * WN, 3)        // three CTAs per SM: 168 registers, 3 x 64 KB of stages
 attention_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out,
@@ -66,9 +82,11 @@ attention_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict_
                      const int* __restrict__ cu_tokens, const int* __restrict__ seq_slots,
                      const int* __restrict__ seq_starts, const int* __restrict__ seq_new,
                      float* __restrict__ part_o, float* __restrict__ part_ml,
-                     int H, int KV, int Gp, float scale_log2, int window, int S) {
+                     int H, int KV, int Gp, float scale_log2, int window, int S, DecodeFuse fuse) {
     pdl_launch_dependents();
-    pdl_wait();
+    // The fused decode form reads only what earlier steps left (the batch's index arrays, the
+    // block table, old cache pages) until it has requested its first page; then it waits.
+    if (!fuse.enabled) pdl_wait();
     constexpr int THREADS = 32 * WM * WN;
     constexpr int ROWS = 16 * WM;
     constexpr int KPW = PAGE / WN;                       // keys of a page that one warp handles
@@ -106,8 +124,69 @@ attention_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict_
         pos[i] = valid[i] ? start + tl : -1;
         lo[i] = (window > 0 && valid[i]) ? max(0, pos[i] - window + 1) : 0;
     }
+    // pages this CTA reads
+    const int last_tok = min(T, t0 + BT) - 1;
+    const int max_pos = start + last_tok;
+    const int min_lo = window > 0 ? max(0, start + t0 - window + 1) : 0;
+    const int first_page = min_lo / PAGE, n_pages = max_pos / PAGE - first_page + 1;
+    const int per = (n_pages + S - 1) / S;
+    const int p_begin = first_page + z * per, p_end = min(first_page + n_pages, p_begin + per);
+    const int* table = block_table + (size_t)slot * blocks_per_seq;
+    const int full_below = start + t0;                   // keys <= this are visible to every valid row (no window)
+
+    auto issue = [&](int page_idx, int st) {
+        const size_t off = ((size_t)table[page_idx] * KV + g) * PAGE * HD;
+        load_page<HD, THREADS>(k_stage + st * PAGE * HD, k_cache + off);
+        load_page<HD, THREADS>(v_stage + st * PAGE * HD, v_cache + off);
+        cp_async_commit();
+    };
+    const bool writes_token = fuse.enabled && p_begin < p_end && p_end == first_page + n_pages;
+    // the first page can be requested now unless it is the one this CTA is about to write into
+    const bool early = p_begin < p_end && !(writes_token && p_begin == p_end - 1);
+    if (fuse.enabled) {
+        if (early) issue(p_begin, 0);
+        pdl_wait();
+    }
     // query fragments
     uint32_t qa[KS][4];
+    const int width = (H + 2 * KV) * HD;
+    auto projected = [&](int token_row, int idx) {       // element idx of a token's q|k|v row, float32
+        if (fuse.n_partials == 0) return to_f32(fuse.qkv[(size_t)token_row * width + idx]);
+        const float* p = fuse.partials + (size_t)token_row * width + idx;
+        float a = 0.f;
+        for (int zz = 0; zz < fuse.n_partials; ++zz) a += p[(size_t)zz * fuse.partial_stride];
+        return a;
+    };
+    if (fuse.enabled) {
+        // q = sum of the pieces, rotated, built once per CTA in shared memory (one pair per thread
+        // and turn), then picked up as fragments.  All valid rows are heads of the sequence's one token.
+        __shared__ __align__(16) bf16 q_sm[16 * HD];
+        const int tpos = start + t0;
+        for (int idx = threadIdx.x; idx < G * (HD / 2); idx += THREADS) {
+            const int hh = idx / (HD / 2), j = idx % (HD / 2);
+            const int base = (g * G + hh) * HD;
+            const float x = projected(row0 + t0, base + j), y = projected(row0 + t0, base + j + HD / 2);
+            float sn, cs;
+            sincosf((float)tpos * fuse.inv_freq[j], &sn, &cs);
+            q_sm[hh * HD + j] = __float2bfloat16_rn(x * cs - y * sn);
+            q_sm[hh * HD + j + HD / 2] = __float2bfloat16_rn(y * cs + x * sn);
+        }
+        __syncthreads();
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                uint32_t x0 = 0u, x1 = 0u;
+                if (valid[i]) {
+                    const bf16* p = q_sm + (quad + 8 * i) * HD + ks * 16 + 2 * tq;       // row r = head r of the group (Gp rows per token)
+                    x0 = *reinterpret_cast<const uint32_t*>(p);
+                    x1 = *reinterpret_cast<const uint32_t*>(p + 8);
+                }
+                qa[ks][i] = x0;
+                qa[ks][2 + i] = x1;
+            }
+        }
+    } else
 #pragma unroll
     for (int ks = 0; ks < KS; ++ks) {
 #pragma unroll
@@ -127,23 +206,22 @@ attention_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict_
     for (int n = 0; n < ON; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 
-    // pages this CTA reads
-    const int last_tok = min(T, t0 + BT) - 1;
-    const int max_pos = start + last_tok;
-    const int min_lo = window > 0 ? max(0, start + t0 - window + 1) : 0;
-    const int first_page = min_lo / PAGE, n_pages = max_pos / PAGE - first_page + 1;
-    const int per = (n_pages + S - 1) / S;
-    const int p_begin = first_page + z * per, p_end = min(first_page + n_pages, p_begin + per);
-    const int* table = block_table + (size_t)slot * blocks_per_seq;
-    const int full_below = start + t0;                   // keys <= this are visible to every valid row (no window)
-
-    auto issue = [&](int page_idx, int st) {
-        const size_t off = ((size_t)table[page_idx] * KV + g) * PAGE * HD;
-        load_page<HD, THREADS>(k_stage + st * PAGE * HD, k_cache + off);
-        load_page<HD, THREADS>(v_stage + st * PAGE * HD, v_cache + off);
-        cp_async_commit();
-    };
-    if (p_begin < p_end) issue(p_begin, 0);
+    if (writes_token) {
+        // this CTA's pages end at the new token: put its rotated key and its value into the cache
+        // first (the token is row0 of the sequence; position max_pos), then read the page as usual
+        const size_t dst = (((size_t)table[max_pos / PAGE] * KV + g) * PAGE + (max_pos % PAGE)) * HD;
+        for (int j = threadIdx.x; j < HD / 2; j += THREADS) {
+            const float x = projected(row0, (H + g) * HD + j), y = projected(row0, (H + g) * HD + j + HD / 2);
+            float sn, cs;
+            sincosf((float)max_pos * fuse.inv_freq[j], &sn, &cs);
+            fuse.k_cache_w[dst + j] = __float2bfloat16_rn(x * cs - y * sn);
+            fuse.k_cache_w[dst + j + HD / 2] = __float2bfloat16_rn(y * cs + x * sn);
+        }
+        for (int j = threadIdx.x; j < HD; j += THREADS)
+            fuse.v_cache_w[dst + j] = __float2bfloat16_rn(projected(row0, (H + KV + g) * HD + j));
+        __syncthreads();                                 // the CTA's own copies below read these rows
+    }
+    if (p_begin < p_end && !(fuse.enabled && early)) issue(p_begin, 0);
     for (int pi = p_begin; pi < p_end; ++pi) {
         const int st = (pi - p_begin) & 1;
         if (pi + 1 < p_end) { issue(pi + 1, st ^ 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
@@ -270,6 +348,35 @@ attention_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict_
                 if (d == 0) { part_ml[(orow * S + z) * 2] = M; part_ml[(orow * S + z) * 2 + 1] = L; }
             }
         }
+        if (fuse.enabled && S > 1) {
+            // The last of the sequence's CTAs (for this kv head) to get here merges the pieces.
+            __shared__ int is_last;
+            __threadfence();
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                const int done = atomicAdd(&fuse.counters[b * KV + g], 1);
+                is_last = done == S - 1;
+                if (is_last) fuse.counters[b * KV + g] = 0;      // zero again for the next launch
+            }
+            __syncthreads();
+            if (is_last) {
+                __threadfence();
+                for (int idx = threadIdx.x; idx < G * HD; idx += THREADS) {
+                    const int hh = idx / HD, d = idx % HD;
+                    const size_t orow = (size_t)row0 * H + (g * G + hh);
+                    float M = -INFINITY;
+                    for (int zz = 0; zz < S; ++zz) M = fmaxf(M, __ldcg(&part_ml[(orow * S + zz) * 2]));
+                    float L = 0.f, acc = 0.f;
+                    for (int zz = 0; zz < S; ++zz) {
+                        const float mz = __ldcg(&part_ml[(orow * S + zz) * 2]);
+                        const float c = mz == -INFINITY ? 0.f : exp2f(mz - M);
+                        L += __ldcg(&part_ml[(orow * S + zz) * 2 + 1]) * c;
+                        acc += __ldcg(&part_o[(orow * S + zz) * HD + d]) * c;
+                    }
+                    out[orow * HD + d] = __float2bfloat16_rn(acc / L);
+                }
+            }
+        }
     } else {
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
@@ -315,7 +422,7 @@ template <int HD, int WM, int WN>
 static int launch_mma(const bf16* q, int q_stride, bf16* out, const bf16* k, const bf16* v, const int* table, int bps,
                       const int* cu, const int* slots, const int* starts, const int* news, float* po, float* pml,
                       int n_seqs, int max_new, int n_rows, int H, int KV, float scale, int window, int S,
-                      cudaStream_t stream) {
+                      const DecodeFuse& fuse, cudaStream_t stream) {
     const int G = H / KV;
     int Gp = 1;
     while (Gp < G) Gp <<= 1;
@@ -332,9 +439,9 @@ static int launch_mma(const bf16* q, int q_stride, bf16* out, const bf16* k, con
         configured = true;
     }
     launch_kernel(attention_mma_kernel<HD, WM, WN>, grid, 32 * WM * WN, smem, stream, q, q_stride, out, k, v, table, bps, cu, slots,
-        starts, news, po, pml, H, KV, Gp, scale * 1.4426950408889634f, window, S);
+        starts, news, po, pml, H, KV, Gp, scale * 1.4426950408889634f, window, S, fuse);
     KL_LAUNCH_CHECK();
-    if (S > 1) {
+    if (S > 1 && !fuse.enabled) {
         launch_kernel(attention_mma_combine_kernel<HD>, dim3(n_rows, H), HD <= 64 ? 32 : 64, 0, stream, po, pml, out, H, S);
         KL_LAUNCH_CHECK();
     }
@@ -350,11 +457,11 @@ using namespace kl;
 // already in the cache.  max_new is the largest seq_new (host copy, sizes the grid); n_rows the
 // number of packed rows.  few_rows != 0 picks the layout for decode (one token per sequence:
 // the warps of a CTA split the keys).  Head sizes 64 and 128; others KL_ERR_BAD_SIZE.
-KL_API int kl_attention_mma(const void* q, int q_stride, void* out, const void* k_cache, const void* v_cache,
+static int attention_mma_dispatch(const void* q, int q_stride, void* out, const void* k_cache, const void* v_cache,
                             const int* block_table, int blocks_per_seq, const int* cu_tokens, const int* seq_slots,
                             const int* seq_starts, const int* seq_new, float* part_o, float* part_ml, int n_seqs,
                             int max_new, int n_rows, int H, int KV, int hd, float scale, int window, int splits,
-                            int few_rows, cudaStream_t stream) {
+                            int few_rows, const DecodeFuse& fuse, cudaStream_t stream) {
     if (n_seqs <= 0 || max_new <= 0) return KL_OK;
     if (KV <= 0 || H % KV || splits < 1) return KL_ERR_BAD_SIZE;
     if (splits > 1 && (part_o == nullptr || part_ml == nullptr)) return KL_ERR_BAD_SIZE;
@@ -362,9 +469,49 @@ KL_API int kl_attention_mma(const void* q, int q_stride, void* out, const void* 
 #define KL_MMA(HD, WM, WN)                                                                                            \
     return launch_mma<HD, WM, WN>((const bf16*)q, q_stride, (bf16*)out, (const bf16*)k_cache, (const bf16*)v_cache,     \
                                   block_table, blocks_per_seq, cu_tokens, seq_slots, seq_starts, seq_new, part_o,      \
-                                  part_ml, n_seqs, max_new, n_rows, H, KV, scale, window, splits, stream)
+                                  part_ml, n_seqs, max_new, n_rows, H, KV, scale, window, splits, fuse, stream)
     if (hd == 128) { if (few_rows) KL_MMA(128, 1, 4); else KL_MMA(128, 4, 1); }
     if (hd == 64) { if (few_rows) KL_MMA(64, 1, 4); else KL_MMA(64, 4, 1); }
 #undef KL_MMA
     return KL_ERR_BAD_SIZE;
+}
+
+KL_API int kl_attention_mma(const void* q, int q_stride, void* out, const void* k_cache, const void* v_cache,
+                            const int* block_table, int blocks_per_seq, const int* cu_tokens, const int* seq_slots,
+                            const int* seq_starts, const int* seq_new, float* part_o, float* part_ml, int n_seqs,
+                            int max_new, int n_rows, int H, int KV, int hd, float scale, int window, int splits,
+                            int few_rows, cudaStream_t stream) {
+    DecodeFuse none;
+    memset(&none, 0, sizeof(none));
+    return attention_mma_dispatch(q, q_stride, out, k_cache, v_cache, block_table, blocks_per_seq, cu_tokens, seq_slots,
+                                  seq_starts, seq_new, part_o, part_ml, n_seqs, max_new, n_rows, H, KV, hd, scale, window,
+                                  splits, few_rows, none, stream);
+}
+
+// A whole decode step's attention in one kernel: one token per sequence, rows in sequence
+// order.  The q/k/v projections come as `qkv` (bfloat16 [rows, (H + 2 KV) * hd]) or as
+// float32 pieces `partials` [n_partials, rows, width]; the kernel rotates q and k (full
+// rotation, inv_freq [hd / 2]), writes the token's key and value into the cache, attends, and
+// merges the splits itself (`counters`: int32 [rows * KV], zero, left zero).
+KL_API int kl_attention_decode_fused(const void* qkv, const float* partials, int n_partials, long long partial_stride,
+                                     const float* inv_freq, void* out, void* k_cache, void* v_cache,
+                                     const int* block_table, int blocks_per_seq, const int* cu_tokens,
+                                     const int* seq_slots, const int* seq_starts, const int* seq_new, float* part_o,
+                                     float* part_ml, int* counters, int n_seqs, int H, int KV, int hd, float scale,
+                                     int window, int splits, cudaStream_t stream) {
+    if (n_seqs <= 0) return KL_OK;
+    if (inv_freq == nullptr || counters == nullptr || (n_partials == 0 && qkv == nullptr)) return KL_ERR_BAD_SIZE;
+    DecodeFuse fuse;
+    fuse.enabled = 1;
+    fuse.partials = partials;
+    fuse.n_partials = n_partials;
+    fuse.partial_stride = (size_t)partial_stride;
+    fuse.qkv = (const bf16*)qkv;
+    fuse.inv_freq = inv_freq;
+    fuse.k_cache_w = (bf16*)k_cache;
+    fuse.v_cache_w = (bf16*)v_cache;
+    fuse.counters = counters;
+    return attention_mma_dispatch(out /* unused as q */, 8, out, k_cache, v_cache, block_table, blocks_per_seq, cu_tokens,
+                                  seq_slots, seq_starts, seq_new, part_o, part_ml, n_seqs, 1, n_seqs, H, KV, hd, scale,
+                                  window, splits, 1, fuse, stream);
 }

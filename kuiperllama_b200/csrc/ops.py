@@ -463,6 +463,62 @@ def matmul_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) -
         gemm_tcgen05(a, w_gate_up, out, swiglu=True)
 
 
+_counters: Dict[int, torch.Tensor] = {}
+
+
+def _zero_counters(device: torch.device, n: int) -> torch.Tensor:
+    """int32 counters that kernels leave at zero (the last CTA of a group resets its own)."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    have = _counters.get(idx)
+    if have is None or have.numel() < n:
+        have = torch.zeros(max(n, 1 << 16), dtype=torch.int32, device=device)
+        _counters[idx] = have
+    return have
+
+
+def decode_fusable(dtype: torch.dtype, head_dim: int, rotary_dim: int, num_heads: int, num_kv_heads: int) -> bool:
+    """Whether a decode step's rotation, cache write, attention and split merge run as one kernel."""
+    return (dtype == torch.bfloat16 and head_dim in MMA_HEAD_DIMS and rotary_dim == head_dim
+            and num_heads % num_kv_heads == 0 and num_heads // num_kv_heads <= 16)
+
+
+def attention_decode_fused(qkv: torch.Tensor, inv_freq: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
+                           v_cache: torch.Tensor, block_table: torch.Tensor, step, num_heads: int, num_kv_heads: int,
+                           head_dim: int, scale: float, window: int = 0, splits: Optional[int] = None) -> None:
+    """One token per sequence (a decode step, rows in sequence order, no padding rows).  ``qkv``
+    is the q/k/v projection, bfloat16 [rows, (H + 2 KV) * hd] or float32 pieces [S, rows, width].
+    Rotates q and k, appends k and v to the cache, attends, merges the splits: one kernel."""
+    _cuda(qkv, inv_freq, out, k_cache, v_cache, block_table)
+    n = step.n_seqs
+    _need(step.is_decode and step.n_tokens == n, "attention_decode_fused: one token per sequence and no padding rows")
+    _need(decode_fusable(out.dtype, head_dim, 2 * inv_freq.numel(), num_heads, num_kv_heads), "attention_decode_fused: not fusable")
+    width = (num_heads + 2 * num_kv_heads) * head_dim
+    parts, plain, n_parts, stride = None, None, 0, 0
+    if qkv.dim() == 3:
+        _need(qkv.dtype == torch.float32 and qkv.is_contiguous() and tuple(qkv.shape[1:]) == (n, width), "attention_decode_fused: pieces")
+        parts, n_parts, stride = qkv, qkv.shape[0], n * width
+    else:
+        _need(qkv.dtype == torch.bfloat16 and qkv.is_contiguous() and tuple(qkv.shape) == (n, width), "attention_decode_fused: qkv")
+        plain = qkv
+    _need(out.is_contiguous() and out.shape[0] >= n and out.shape[1] == num_heads * head_dim, "attention_decode_fused: out shape")
+    _need(k_cache.is_contiguous() and v_cache.is_contiguous() and k_cache.dtype == torch.bfloat16
+          and tuple(k_cache.shape[1:]) == (num_kv_heads, PAGE, head_dim), "attention_decode_fused: cache layout")
+    _need(inv_freq.dtype == torch.float32 and inv_freq.numel() == head_dim // 2, "attention_decode_fused: inv_freq")
+    if splits is None:
+        ctas = max(1, n * num_kv_heads)
+        splits = max(1, min(16, (2 * SM_COUNT + ctas - 1) // ctas))
+    po = pml = None
+    if splits > 1:
+        po = torch.empty((n, num_heads, splits, head_dim), dtype=torch.float32, device=out.device)
+        pml = torch.empty((n, num_heads, splits, 2), dtype=torch.float32, device=out.device)
+    counters = _zero_counters(out.device, n * num_kv_heads)
+    _check(lib("attention_mma").kl_attention_decode_fused(
+        _ptr(plain), _ptr(parts), n_parts, ctypes.c_longlong(stride), _ptr(inv_freq), _ptr(out), _ptr(k_cache), _ptr(v_cache),
+        _ptr(block_table), block_table.shape[1], _ptr(step.cu_tokens), _ptr(step.seq_slots), _ptr(step.seq_starts),
+        _ptr(step.seq_new), _ptr(po), _ptr(pml), _ptr(counters), n, num_heads, num_kv_heads, head_dim, ctypes.c_float(scale),
+        int(window or 0), splits, _stream()), "attention_decode_fused")
+
+
 # Which kernel decode steps of the bfloat16 path use when both fit: "mma" (tensor cores) or
 # "simt" (attention_decode.cu).
 DECODE_KERNEL = "mma"

@@ -60,6 +60,13 @@ class AttentionMixer(Mixer):
     def forward(self, x: torch.Tensor, step: StepContext, cache: CacheView) -> torch.Tensor:
         n = step.n_tokens
         qkv = self.qkv.forward(x, allow_partials=True)
+        if (step.is_decode and cache.writable and n == step.n_seqs and self.inv_freq is not None
+                and ops.decode_fusable(self.runtime.dtype, self.hd, self.rotary_dim, self.H, self.KV)):
+            # a decode step: rotation, cache write, attention and the merge of the splits in one kernel
+            attn = torch.empty((n, self.H * self.hd), dtype=self.runtime.dtype, device=x.device)
+            ops.attention_decode_fused(qkv, self.inv_freq, attn, cache.k, cache.v, cache.block_table, step, self.H, self.KV,
+                                       self.hd, self.scale, int(self.window or 0))
+            return self.o.forward(attn, allow_partials=True)
         parts = None
         if qkv.dim() == 3:                                         # pieces of the product: the rotary kernel adds them
             parts, qkv = qkv, torch.empty(qkv.shape[1:], dtype=self.runtime.dtype, device=x.device)

@@ -549,3 +549,46 @@ def test_gate_up_product_with_swiglu_epilogue(ops, M, I, K):
     ref = g / (1 + torch.exp(-g)) * u
     err = float((out.double().cpu() - ref).abs().max())
     assert err <= 8e-3 * float(ref.abs().max()) + 1e-6, f"fused swiglu {M}x{I}x{K}: error {err:.3e}"
+
+
+@pytest.mark.parametrize("H,KV,hd,window,splits,pieces", [(8, 2, 128, 0, 1, 0), (32, 8, 128, 0, 5, 6), (4, 4, 64, 0, 3, 2),
+                                                          (6, 2, 64, 0, 16, 0), (8, 8, 128, 100, 2, 3), (16, 1, 128, 0, 4, 1)])
+def test_attention_decode_fused(ops, H, KV, hd, window, splits, pieces):
+    """Rotation of q and k, the cache write, attention and the split merge in one kernel, against
+    the separate rotary kernel followed by the reference attention; twice, so that the counters
+    the kernel leaves behind are shown to be zero again."""
+    from types import SimpleNamespace
+    seqs = [(199, 1), (0, 1), (64, 1), (128, 1), (63, 1), (249, 1), (1000, 1)]
+    cache, slots, ks, vs, qbuf, stride, cu, sl, st, nw, rows = _ragged_problem(H, KV, hd, seqs, seed=19)
+    inv = plain_llama.rope_inverse_frequencies(hd, 500000.0, None).to(DEV)
+    scale = 1 / math.sqrt(hd)
+    for round_ in range(2):
+        torch.manual_seed(20 + round_)
+        qkv = torch.randn(rows, stride, device=DEV).bfloat16()
+        step = SimpleNamespace(n_seqs=rows, n_tokens=rows, is_decode=True, cu_tokens=cu, seq_slots=sl, seq_starts=st, seq_new=nw)
+        arg = qkv
+        if pieces:
+            parts = torch.randn(pieces, rows, stride, device=DEV)
+            parts[-1] = qkv.float() - parts[:-1].sum(0)
+            arg = parts.contiguous()
+            exact = parts[0].clone()
+            for z in range(1, pieces):
+                exact += parts[z]
+        else:
+            exact = qkv.float()
+        out = torch.full((rows, H * hd), 3.0, device=DEV, dtype=torch.bfloat16)
+        ops.attention_decode_fused(arg, inv, out, cache.k, cache.v, cache.table, step, H, KV, hd, scale, window, splits)
+        e = exact.cpu().view(rows, H + 2 * KV, hd)
+        for i, (s0, _) in enumerate(seqs):
+            p = torch.tensor([s0])
+            qr = plain_llama.rope_rotate(e[i:i + 1, :H], p, inv.cpu())[0].bfloat16().float()
+            kr = plain_llama.rope_rotate(e[i:i + 1, H:H + KV], p, inv.cpu())[0]
+            kk = torch.cat([ks[i][:s0], kr[None]], 0).bfloat16().float()
+            vv = torch.cat([vs[i][:s0], e[i:i + 1, H + KV:]], 0).bfloat16().float()
+            ref = _ref_attention(qr, kk, vv, s0, scale, window)
+            _close(out[i].view(H, hd), ref, "bfloat16", f"fused decode seq {i} round {round_}", scale=float(vv.abs().max()))
+            got_k = cache.rows("k", slots[i], s0 + 1)[s0]
+            got_v = cache.rows("v", slots[i], s0 + 1)[s0]
+            _close(got_k, kr, "bfloat16", f"new key of seq {i}", scale=float(e.abs().max()))
+            _close(got_v, e[i, H + KV:], "bfloat16", f"new value of seq {i}", scale=float(e.abs().max()))
+    assert int(ops._zero_counters(torch.device(DEV), 1).abs().sum()) == 0
