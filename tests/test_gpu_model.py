@@ -230,3 +230,35 @@ def test_decode_steps_replayed_from_cuda_graphs(model_folders, name, dtype):
         assert sorted(engine._graphs) == [1, 2, 3]
         from kuiperllama_b200.csrc import ops
         ops.check_status(torch.device("cuda:0"))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_llama31_8b_layer_sizes_one_layer(tmp_path_factory, dtype):
+    """One layer with the widths of Llama-3.1-8B (hidden 4096, 32 heads, 8 kv heads, head size
+    128, intermediate 14336, llama3 rope scaling) and a cut vocabulary: the tensor-core kernels
+    at the shapes they serve, against the plain implementation, whole and one by one."""
+    from helpers import write_folder, TINY
+    from kuiperllama_b200.engine import Engine, SequenceInput, load_model
+    TINY["wide"] = {
+        "architectures": ["LlamaForCausalLM"], "hidden_size": 4096, "intermediate_size": 14336, "num_hidden_layers": 1,
+        "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128, "vocab_size": 2000,
+        "max_position_embeddings": 4096, "rms_norm_eps": 1e-5, "rope_theta": 500000.0,
+        "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                         "original_max_position_embeddings": 8192},
+        "tie_word_embeddings": False, "hidden_act": "silu",
+    }
+    folder = str(tmp_path_factory.mktemp("wide"))
+    write_folder(folder, "wide", seed=7)
+    tokens = random_tokens(150, 2000, seed=900)
+    ref = plain_logits(folder, tokens)
+    with torch.inference_mode():
+        model = load_model(folder, dtype=dtype, device="cuda:0")
+        engine = Engine(model, model.new_cache(max_tokens=64 * 8), use_graphs=(dtype == "bfloat16"))
+        slot = engine.alloc_slot()
+        got = [engine.step([SequenceInput(slot, tokens[:140], list(range(140)))])]
+        for t in tokens[140:]:
+            got.append(engine.decode_step([slot], [t]).clone())
+        engine.free_slot(slot)
+    assert_close(torch.cat(got), ref, dtype, f"8B-width layer, {dtype}")
+    from kuiperllama_b200.csrc import ops
+    ops.check_status(torch.device("cuda:0"))

@@ -276,3 +276,97 @@ def test_an_execution_can_read_another_executions_cache():
         got += [engine.step([SequenceInput(slot, [t], [0])]) for t in tokens[66:]]
         engine.free_slot(slot)
     assert_close(torch.cat(got), ref, "float32", "cache read from another execution")
+
+
+def test_toy_feed_forward_with_routing_and_toy_position_encoding():
+    """Two more kinds of parts defined outside the package: a feed-forward that routes every token
+    to one of three small experts (router logits in float32), and a learned absolute position
+    encoding that is added to the embeddings.  Registered, built from a ModelSpec and stepped
+    whole and token by token through the unchanged engine."""
+    from kuiperllama_b200.config import PartSpec, config_from_dict
+    from kuiperllama_b200.engine import DecoderModel, Engine, SequenceInput, model_manifest
+    from kuiperllama_b200.parts import FeedForward, PositionEncoding, Runtime, register_feed_forward, register_position
+    from kuiperllama_b200.weights import TensorDecl
+    from kuiperllama_b200.weights.random_init import random_tensor
+
+    @register_feed_forward("toy_top1_experts")
+    class Top1Experts(FeedForward):
+        @classmethod
+        def manifest(cls, spec, prefix):
+            h, e, i = spec["hidden_size"], spec["experts"], spec["inner"]
+            m = {prefix + "moe.router": TensorDecl((e, h), role="vector")}
+            for k in range(e):
+                m[prefix + f"moe.{k}.up"] = TensorDecl((i, h))
+                m[prefix + f"moe.{k}.down"] = TensorDecl((h, i))
+            return m
+
+        def __init__(self, spec, prefix, tensors, runtime):
+            super().__init__(spec, prefix, tensors, runtime)
+            e = spec["experts"]
+            self.router = tensors[prefix + "moe.router"].to(runtime.device, torch.float32)
+            self.up = [tensors[prefix + f"moe.{k}.up"].to(runtime.device, torch.float32) for k in range(e)]
+            self.down = [tensors[prefix + f"moe.{k}.down"].to(runtime.device, torch.float32) for k in range(e)]
+
+        def forward(self, x, step):
+            xf = x.float()
+            choice = (xf @ self.router.T).argmax(dim=-1)                 # float32 router logits
+            out = torch.zeros_like(xf)
+            for k in range(len(self.up)):
+                rows = (choice == k).nonzero().flatten()
+                if rows.numel():
+                    out[rows] = torch.relu(xf[rows] @ self.up[k].T) @ self.down[k].T
+            return out.to(x.dtype)
+
+    @register_position("toy_learned_absolute")
+    class LearnedAbsolute(PositionEncoding):
+        @classmethod
+        def manifest(cls, spec, prefix):
+            return {prefix + "pos.table": TensorDecl((spec["positions"], spec["hidden_size"]), role="vector")}
+
+        def __init__(self, spec, prefix, tensors, runtime):
+            super().__init__(spec, prefix, tensors, runtime)
+            self.table = tensors[prefix + "pos.table"].to(runtime.device, torch.float32)
+
+        def add_to_embeddings(self, residual, step):
+            residual[:step.n_tokens] += self.table[step.positions[:step.n_tokens].long()]
+
+    cfg = config_from_dict(config_dict("tiny1"))
+    spec = cfg.to_model_spec()
+    layers = list(spec.layers)
+    pos = PartSpec("toy_learned_absolute", {"positions": 128, "hidden_size": cfg.hidden_size})
+    ffn = PartSpec("toy_top1_experts", {"hidden_size": cfg.hidden_size, "experts": 3, "inner": 40})
+    layers[0] = dataclasses.replace(layers[0], position=pos)               # no rotation in layer 0: absolute table instead
+    layers[1] = dataclasses.replace(layers[1], feed_forward=ffn)
+    spec = dataclasses.replace(spec, layers=tuple(layers))
+    manifest = model_manifest(spec)
+    assert "model.layers.0.pos.table" in manifest and "model.layers.1.moe.2.down" in manifest
+    assert "model.layers.1.mlp.gate_proj.weight" not in manifest
+    tensors = {n: random_tensor(n, d, seed=8, std=0.05) for n, d in manifest.items()}
+    model = DecoderModel(spec, tensors, Runtime(DEV, torch.float32))
+    engine = Engine(model, model.new_cache(max_tokens=64 * 4))
+    w = {k: v.float() for k, v in tensors.items()}
+    c = dict(config_dict("tiny1"), head_dim=cfg.head_dim)
+    tokens = random_tokens(40, cfg.vocab_size, seed=60)
+    # the same model with the plain implementation's functions
+    inv = plain_llama.rope_inverse_frequencies(c["head_dim"], c["rope_theta"], None)
+    x = plain_llama.embedding(w["model.embed_tokens.weight"], tokens) + w["model.layers.0.pos.table"][:40]
+    for layer in (0, 1):
+        p = f"model.layers.{layer}."
+        n = plain_llama.rmsnorm(x, w[p + "input_layernorm.weight"], c["rms_norm_eps"])
+        no_rotation = torch.zeros_like(inv)                                 # angle 0: layer 0 has no rotary part
+        x = x + plain_llama.attention_mixer(n, w, p, c, no_rotation if layer == 0 else inv)
+        n = plain_llama.rmsnorm(x, w[p + "post_attention_layernorm.weight"], c["rms_norm_eps"])
+        if layer == 1:
+            choice = (n @ w[p + "moe.router"].T).argmax(-1)
+            f = torch.stack([torch.relu(n[t] @ w[p + f"moe.{int(choice[t])}.up"].T) @ w[p + f"moe.{int(choice[t])}.down"].T
+                             for t in range(40)])
+        else:
+            f = plain_llama.swiglu_feed_forward(n, w, p)
+        x = x + f
+    ref = plain_llama.output_logits(x, w, c)
+    with torch.inference_mode():
+        slot = engine.alloc_slot()
+        got = [engine.step([SequenceInput(slot, tokens[:33], list(range(33)))])]
+        got += [engine.step([SequenceInput(slot, [t], [0])]) for t in tokens[33:]]
+        engine.free_slot(slot)
+    assert_close(torch.cat(got), ref, "float32", "toy routed feed-forward and absolute positions")
