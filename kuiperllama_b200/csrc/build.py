@@ -30,11 +30,12 @@ SOURCES: Dict[str, str] = {
     "attention_simt": "attention_simt.cu",
     "attention_decode": "attention_decode.cu",
     "attention_mma": "attention_mma.cu",
+    "attention_tcgen05": "attention_tcgen05.cu",
     "gemm_simt": "gemm_simt.cu",
     "gemm_tcgen05": "gemm_tcgen05.cu",
     "sampling": "sampling.cu",
 }
-HEADERS: List[str] = ["common.cuh", "attention_decode_noalloc.h"]
+HEADERS: List[str] = ["common.cuh", "tcgen05.cuh", "tma_host.cuh", "attention_decode_noalloc.h"]
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-shared", "--expt-relaxed-constexpr", "--extended-lambda"]

@@ -3,7 +3,7 @@ repeats, a buffer larger than L2 written between repeats), and print the achieve
 
     python -m kuiperllama_b200.csrc.microbench gemm_skinny --m 8 --n 28672 --k 4096 [--swiglu]
     python -m kuiperllama_b200.csrc.microbench gemm_tcgen05 --m 2048 --n 6144 --k 4096
-    python -m kuiperllama_b200.csrc.microbench attention_prefill --tokens 2048 --heads 32 --kv-heads 8 --head-dim 128
+    python -m kuiperllama_b200.csrc.microbench attention_prefill --tokens 2048 --heads 32 --kv-heads 8 --head-dim 128 [--mma]
     python -m kuiperllama_b200.csrc.microbench attention_decode --batch 64 --context 640 --heads 32 --kv-heads 8 --head-dim 128
 
 It is also the small case that profiler captures of single kernels are taken on.
@@ -66,6 +66,7 @@ def main(argv=None) -> int:
     ap.add_argument("--head-dim", type=int, default=128)
     ap.add_argument("--repeats", type=int, default=20)
     ap.add_argument("--simt", action="store_true", help="attention_decode: the split-KV SIMT kernel instead of the tensor-core one")
+    ap.add_argument("--mma", action="store_true", help="attention_prefill: the mma.sync kernel instead of the tcgen05 one")
     args = ap.parse_args(argv)
     torch.manual_seed(0)
     out = {"kernel": args.kernel}
@@ -92,7 +93,10 @@ def main(argv=None) -> int:
             q = torch.randn(T, (H + 2 * KV) * hd, device=DEV).bfloat16()
             o = torch.empty(T, H * hd, device=DEV, dtype=torch.bfloat16)
             cu, sl, st, nw = i32([0, T]), i32([0]), i32([0]), i32([T])
-            fn = lambda: ops.attention_mma(q, q.shape[1], o, k, v, table, cu, sl, st, nw, 1, T, T, H, KV, hd, scale, 0, 1, False)
+            if args.mma or hd != 128:
+                fn = lambda: ops.attention_mma(q, q.shape[1], o, k, v, table, cu, sl, st, nw, 1, T, T, H, KV, hd, scale, 0, 1, False)
+            else:
+                fn = lambda: ops.attention_tcgen05(q, q.shape[1], o, k, v, table, cu, sl, st, nw, 1, T, T, H, KV, hd, scale)
             t = _time(fn, args.repeats)
             flops = 4.0 * H * hd * T * (T + 1) / 2
             out.update(tokens=T, heads=H, kv_heads=KV, head_dim=hd, us=round(t * 1e6, 2), tflops=round(flops / t / 1e12, 1))

@@ -463,6 +463,32 @@ def matmul_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) -
         gemm_tcgen05(a, w_gate_up, out, swiglu=True)
 
 
+def attention_tcgen05(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                      block_table: torch.Tensor, cu_tokens: torch.Tensor, seq_slots: torch.Tensor, seq_starts: torch.Tensor,
+                      seq_new: torch.Tensor, n_seqs: int, max_new: int, n_rows: int, num_heads: int, num_kv_heads: int,
+                      head_dim: int, scale: float) -> None:
+    """Prefill attention with both products on tcgen05 (bfloat16, head size 128, no window)."""
+    _cuda(q, out, k_cache, v_cache, block_table, cu_tokens, seq_slots, seq_starts, seq_new)
+    for t, nm in ((block_table, "block_table"), (cu_tokens, "cu_tokens"), (seq_slots, "seq_slots"),
+                  (seq_starts, "seq_starts"), (seq_new, "seq_new")):
+        _i32(t, nm)
+    _need(q.dtype == out.dtype == k_cache.dtype == v_cache.dtype == torch.bfloat16, "attention_tcgen05: bfloat16 only")
+    _need(head_dim == 128 and q_stride % 8 == 0 and q.data_ptr() % 16 == 0, "attention_tcgen05: head_dim 128, aligned rows")
+    _need(out.is_contiguous() and out.shape[0] >= n_rows and out.shape[1] == num_heads * head_dim, "attention_tcgen05: out shape")
+    _need(k_cache.is_contiguous() and v_cache.is_contiguous()
+          and tuple(k_cache.shape[1:]) == (num_kv_heads, PAGE, head_dim), "attention_tcgen05: cache layout")
+    _need(q.shape[0] >= n_rows, "attention_tcgen05: q rows")
+    cache_rows = k_cache.shape[0] * num_kv_heads * PAGE
+    _check(lib("attention_tcgen05").kl_attention_tcgen05(
+        _ptr(q), q_stride, _ptr(out), _ptr(k_cache), _ptr(v_cache), ctypes.c_longlong(cache_rows), _ptr(block_table),
+        block_table.shape[1], _ptr(cu_tokens), _ptr(seq_slots), _ptr(seq_starts), _ptr(seq_new), n_seqs, max_new,
+        q.shape[0], num_heads, num_kv_heads, head_dim, ctypes.c_float(scale), _ptr(status_word(q.device)), _stream()),
+        "attention_tcgen05")
+
+
+# Which kernel prefill steps of the bfloat16 path use for head size 128: "tcgen05" or "mma".
+PREFILL_KERNEL = "tcgen05"
+
 _counters: Dict[int, torch.Tensor] = {}
 
 
@@ -532,7 +558,11 @@ def attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache: torch.
     sizes, the split-KV kernel; float32 and everything else takes the plain kernel."""
     bf = q.dtype == torch.bfloat16
     group = num_heads // num_kv_heads
-    if bf and head_dim in MMA_HEAD_DIMS and group <= 16 and (not step.is_decode or DECODE_KERNEL == "mma"):
+    if (bf and not step.is_decode and PREFILL_KERNEL == "tcgen05" and head_dim == 128 and not window and group <= 128
+            and q_stride % 8 == 0 and q.data_ptr() % 16 == 0 and step.max_new >= 8):
+        attention_tcgen05(q, q_stride, out, k_cache, v_cache, block_table, step.cu_tokens, step.seq_slots, step.seq_starts,
+                          step.seq_new, step.n_seqs, step.max_new, step.n_tokens, num_heads, num_kv_heads, head_dim, scale)
+    elif bf and head_dim in MMA_HEAD_DIMS and group <= 16 and (not step.is_decode or DECODE_KERNEL == "mma"):
         splits = 1
         if step.is_decode:
             ctas = max(1, step.n_seqs * num_kv_heads)

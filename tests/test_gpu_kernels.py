@@ -592,3 +592,49 @@ def test_attention_decode_fused(ops, H, KV, hd, window, splits, pieces):
             _close(got_k, kr, "bfloat16", f"new key of seq {i}", scale=float(e.abs().max()))
             _close(got_v, e[i, H + KV:], "bfloat16", f"new value of seq {i}", scale=float(e.abs().max()))
     assert int(ops._zero_counters(torch.device(DEV), 1).abs().sum()) == 0
+
+
+@pytest.mark.parametrize("H,KV", [(8, 2), (32, 8), (4, 4), (6, 2), (8, 1), (16, 1)])
+def test_attention_tcgen05_prefill(ops, H, KV):
+    hd = 128
+    seqs = [(0, 150), (0, 1), (60, 70), (3, 64), (0, 65), (100, 5), (0, 300)]
+    cache, slots, ks, vs, qbuf, stride, cu, sl, st, nw, rows = _ragged_problem(H, KV, hd, seqs, seed=21)
+    out = torch.full((rows + 2, H * hd), 3.0, device=DEV, dtype=torch.bfloat16)
+    scale = 1 / math.sqrt(hd)
+    ops.attention_tcgen05(qbuf, stride, out, cache.k, cache.v, cache.table, cu, sl, st, nw, len(seqs), max(t for _, t in seqs),
+                          rows, H, KV, hd, scale)
+    ops.check_status(out.device)
+    assert float((out[rows:].float() - 3.0).abs().max()) == 0.0, "a padding row was written"
+    r = 0
+    for i, (s0, t) in enumerate(seqs):
+        kk, vv = ks[i].bfloat16().float(), vs[i].bfloat16().float()
+        for j in range(t):
+            qv = qbuf[r, :H * hd].float().cpu().view(H, hd)
+            ref = _ref_attention(qv, kk, vv, s0 + j, scale, 0)
+            _close(out[r].view(H, hd), ref, "bfloat16", f"tcgen05 prefill seq {i} token {j}", scale=float(vv.abs().max()))
+            r += 1
+
+
+def test_attention_tcgen05_finds_one_far_key_among_thousands(ops):
+    torch.manual_seed(22)
+    dt = torch.bfloat16
+    H, KV, hd, n, new = 8, 2, 128, 3000, 40
+    for far in (0, 63, 64, 127, 128, 1999, 2999):
+        cache = Paged(2, 3072, KV, hd, dt, seed=7)
+        k = torch.randn(n, KV, hd) * 0.1
+        v = torch.randn(n, KV, hd)
+        k[far] = 0
+        k[far, :, 9] = 40.0
+        _fill_cache(cache, 1, k, v)
+        q = torch.randn(new, H, hd) * 0.1
+        q[:, :, 9] = 40.0
+        qbuf = q.view(new, H * hd).to(dt).to(DEV)
+        out = torch.empty(new, H * hd, device=DEV, dtype=dt)
+        i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+        ops.attention_tcgen05(qbuf, H * hd, out, cache.k, cache.v, cache.table, i32([0, new]), i32([1]), i32([n - new]), i32([new]),
+                              1, new, new, H, KV, hd, 1 / math.sqrt(hd))
+        ops.check_status(out.device)
+        want = v[far].to(dt).float().repeat_interleave(H // KV, dim=0)
+        for j in range(new):
+            if far <= n - new + j:
+                _close(out[j].view(H, hd), want, "bfloat16", f"far key at {far}, query {j}")
