@@ -38,6 +38,11 @@ __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, u
                  : : "r"(smem_u32(dst)), "l"((uint64_t)map), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z) : "memory");
 }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 
 // MN-major operand with the 128-byte swizzle: rows (k) of 128 bytes hold 64 consecutive
 // elements of the MN dimension; 8 rows are 1024 bytes apart (stride byte offset); the next 64
@@ -197,38 +202,48 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             tc_fence_after();
             const int keys = min(2, n_pages - 2 * j) * PAGE;
             const int key0 = 2 * j * PAGE;
-            const bool need_mask = key0 + keys - 1 > start + t0 || !valid;
-            // pass 1: the row's maximum
+            // The same for all lanes of the warp: the tensor-memory loads below are warp-wide
+            // instructions and must not sit in branches that lanes take differently.
+            const bool need_mask = key0 + keys - 1 > start + t0 || __any_sync(0xffffffffu, !valid);
+            // pass 1: the row's maximum of the raw scores (the scale is positive: it commutes with max)
             float mx = -INFINITY;
             uint32_t c32[32];
-            for (int c = 0; c < keys; c += 32) {
-                tmem_ld32(lane_base + s * 128 + c, c32);
-                tmem_ld_wait();
+            if (need_mask) {
+                for (int c = 0; c < keys; c += 32) {
+                    tmem_ld32(lane_base + s * 128 + c, c32);
+                    tmem_ld_wait();
+                    const int visible = pos - key0 - c;            // elements 0..visible are seen
 #pragma unroll
-                for (int e = 0; e < 32; ++e) {
-                    float v = __uint_as_float(c32[e]) * args.scale_log2;
-                    if (need_mask && key0 + c + e > pos) v = -INFINITY;
-                    mx = fmaxf(mx, v);
+                    for (int e = 0; e < 32; ++e) mx = fmaxf(mx, e <= visible ? __uint_as_float(c32[e]) : -INFINITY);
+                }
+            } else {
+                for (int c = 0; c < keys; c += 32) {
+                    tmem_ld32(lane_base + s * 128 + c, c32);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int e = 0; e < 32; e += 2) mx = fmaxf(mx, fmaxf(__uint_as_float(c32[e]), __uint_as_float(c32[e + 1])));
                 }
             }
-            const float m_new = fmaxf(m, mx);
+            const float m_new = fmaxf(m, mx * args.scale_log2);
             const float muse = m_new == -INFINITY ? 0.f : m_new;
-            const float corr = exp2f(m - muse);
-            // pass 2: probabilities, their sum, and the bfloat16 tile for the second product
+            const float corr = fast_exp2(m - muse);
+            // pass 2: probabilities exp2(score * scale - max), their sum, and the bfloat16 tile for
+            // the second product
             float sum = 0.f;
             uint8_t* prow = p_sm + s * AT_P_BYTES + r * 128;
             for (int c = 0; c < keys; c += 32) {
                 tmem_ld32(lane_base + s * 128 + c, c32);
                 tmem_ld_wait();
                 uint32_t packed[16];
+                const int visible = need_mask ? pos - key0 - c : 32;
 #pragma unroll
                 for (int e = 0; e < 32; e += 2) {
-                    float v0 = __uint_as_float(c32[e]) * args.scale_log2, v1 = __uint_as_float(c32[e + 1]) * args.scale_log2;
+                    float p0 = fast_exp2(fmaf(__uint_as_float(c32[e]), args.scale_log2, -muse));
+                    float p1 = fast_exp2(fmaf(__uint_as_float(c32[e + 1]), args.scale_log2, -muse));
                     if (need_mask) {
-                        if (key0 + c + e > pos) v0 = -INFINITY;
-                        if (key0 + c + e + 1 > pos) v1 = -INFINITY;
+                        if (e > visible) p0 = 0.f;
+                        if (e + 1 > visible) p1 = 0.f;
                     }
-                    const float p0 = exp2f(v0 - muse), p1 = exp2f(v1 - muse);
                     sum += p0 + p1;
                     __nv_bfloat162 pr = __floats2bfloat162_rn(p0, p1);
                     packed[e >> 1] = *reinterpret_cast<uint32_t*>(&pr);

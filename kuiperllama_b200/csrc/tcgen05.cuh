@@ -7,7 +7,7 @@
 
 namespace kl {
 
-constexpr uint32_t SPIN_LIMIT = 1u << 26;
+constexpr uint32_t SPIN_LIMIT = 1u << 22;     // polls before a wait gives up (a fraction of a second)
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
