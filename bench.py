@@ -205,7 +205,8 @@ def time_e2e(infer, batch, steps, seed):
 def reference_arm(args):
     """ExiledOfCode/KuiperLLama is a CMake C++ project without a Python package definition, and
     its build fetches glog, armadillo, sentencepiece and gtest over the network; it cannot be
-    installed offline (see DESIGN.md for the recorded attempt)."""
+    installed offline: `pip install --no-index` answers that the directory has neither
+    setup.py nor pyproject.toml."""
     print(json.dumps({"impl": "reference", "unavailable":
                       "KuiperLLama has no setup.py/pyproject.toml (pip install fails) and its CMake build needs "
                       "glog, armadillo, sentencepiece and gtest fetched from the network"}))

@@ -82,7 +82,9 @@ def reference_logits(ref, c, w, tokens):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_golden.py /path/to/KuiperLLama")
+    ref_root = sys.argv[1]
     spec = importlib.util.spec_from_file_location("kuiper_tools_model", os.path.join(ref_root, "tools", "model.py"))
     ref = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(ref)
