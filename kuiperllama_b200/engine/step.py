@@ -18,7 +18,7 @@ from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
 
-from ..cache import CacheError, SequenceCache
+from ..cache import PAGE, CacheError, SequenceCache
 from ..parts.base import StepContext
 from .model import DecoderModel
 
@@ -183,15 +183,17 @@ class Engine:
         time it runs and replayed afterwards: the same kernels on the same buffers with one
         launch.  The logits tensor of a replayed step is the graph's own output buffer; it is
         overwritten by the next decode step of the same batch size."""
-        inputs = [SequenceInput(s, [int(t)], [0]) for s, t in zip(slots, tokens)]
         if not self.use_graphs:
-            return self.step(inputs)
+            return self.step([SequenceInput(s, [int(t)], [0]) for s, t in zip(slots, tokens)])
         from ..csrc import ops
-        n = len(inputs)
-        ctx, want_rows, _ = self._pack(inputs, 0)
+        n = len(slots)
         g = self._graphs.get(n)
-        if g is not None and g.staging_ptr != self._staging.dev.data_ptr():
-            self._graphs.clear()                          # the staging buffer moved: captured addresses are stale
+        if g is not None and self._staging is not None and g.staging_ptr == self._staging.dev.data_ptr():
+            return self._replay(g, list(slots), [int(t) for t in tokens])
+        inputs = [SequenceInput(s, [int(t)], [0]) for s, t in zip(slots, tokens)]
+        ctx, want_rows, _ = self._pack(inputs, 0)
+        if g is not None:                                 # the staging buffer moved: captured addresses are stale
+            self._graphs.clear()
             g = None
         if g is None:
             # The first step of this size runs eagerly (it also warms every kernel up); then the
@@ -214,6 +216,36 @@ class Engine:
         for s, st in zip(inputs, ctx.host_starts):
             self.cache.lengths[s.slot] = st + 1
         return logits
+
+    def _replay(self, g: _DecodeGraph, slots: List[int], tokens: List[int]) -> torch.Tensor:
+        """The short way through a decode step whose graph exists: the same checks and the same
+        staging layout as ``_pack`` for one token per sequence, then one graph launch."""
+        from ..csrc import ops
+        n = len(slots)
+        cache, lengths = self.cache, self.cache.lengths
+        if len(set(slots)) != n:
+            raise StepError("a slot appears twice in one step")
+        if min(tokens) < 0 or max(tokens) >= self.model.spec.vocab_size:
+            raise StepError(f"a token id is outside the vocabulary of {self.model.spec.vocab_size}")
+        starts = []
+        for s in slots:
+            if not cache.slots.is_held(s):
+                raise StepError(f"slot {s} is not held by a sequence")
+            st = lengths[s]
+            if st % PAGE == 0 or st + 1 > cache.max_seq_len:      # a new page, or the limit: let the cache decide
+                try:
+                    cache.reserve(s, st + 1)
+                except CacheError as e:
+                    raise StepError(str(e)) from None
+            starts.append(st)
+        cache.flush_tables()
+        # ids | positions | token_slot | slots | starts | news | cu | want
+        self._staging.upload(tokens + starts + slots + slots + starts + [1] * n + list(range(n + 1)) + list(range(n)))
+        g.graph.replay()
+        ops.launch_count += g.launches
+        for s, st in zip(slots, starts):
+            lengths[s] = st + 1
+        return g.logits
 
     def check_device_errors(self) -> None:
         """Synchronises and raises if a kernel flagged a token id outside the vocabulary."""
