@@ -8,8 +8,8 @@
 //
 // A CTA owns 16 * WM query rows of one sequence and one kv head; a row is (token, head of the
 // kv group), so the group's heads share every key and value that is loaded.  Keys and values
-// come a cache page (64 keys) at a time through cp.async into shared memory, double
-// buffered and XOR-swizzled so that ldmatrix is free of bank conflicts.  Each warp keeps its
+// come a cache page (64 keys) at a time through cp.async into a ring of shared-memory stages
+// (two here; the count is a template parameter), XOR-swizzled so that ldmatrix is free of bank conflicts.  Each warp keeps its
 // 16 rows' queries as mma.sync A fragments, multiplies them with the page's keys (B fragments
 // by ldmatrix), runs the online softmax on the score fragments in registers, and multiplies
 // the probabilities (converted in place to A fragments) with the values (ldmatrix.trans).
@@ -74,8 +74,8 @@ struct DecodeFuse {
     int* counters;                // [rows * KV], zero
 };
 
-template <int HD, int WM, int WN>
-__global__ void __launch_bounds__(32 * WM * WN, 3)        // three CTAs per SM: 168 registers, 3 x 64 KB of stages
+template <int HD, int WM, int WN, int NS>
+__global__ void __launch_bounds__(32 * WM * WN, NS == 2 ? 3 : 2)   // NS = 2: three CTAs per SM (168 registers, 3 x 64 KB of stages)
 attention_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out,
                      const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                      const int* __restrict__ block_table, int blocks_per_seq,
@@ -94,8 +94,8 @@ attention_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict_
     constexpr int KS = HD / 16;                          // k steps of q . k
     constexpr int ON = HD / 8;                           // output tiles (8 dims each)
     extern __shared__ __align__(128) uint8_t smem_raw[];
-    bf16* k_stage = reinterpret_cast<bf16*>(smem_raw);                   // [2][64][HD]
-    bf16* v_stage = k_stage + 2 * PAGE * HD;                             // [2][64][HD]
+    bf16* k_stage = reinterpret_cast<bf16*>(smem_raw);                   // [NS][64][HD]
+    bf16* v_stage = k_stage + NS * PAGE * HD;                            // [NS][64][HD]
 
     const int b = blockIdx.y;
     const int g = blockIdx.z % KV, z = blockIdx.z / KV;
@@ -141,10 +141,13 @@ attention_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict_
         cp_async_commit();
     };
     const bool writes_token = fuse.enabled && p_begin < p_end && p_end == first_page + n_pages;
-    // the first page can be requested now unless it is the one this CTA is about to write into
-    const bool early = p_begin < p_end && !(writes_token && p_begin == p_end - 1);
+    // Pages are requested NS - 1 ahead, one cp.async group per page in page order.  The fused
+    // decode form requests what it can before it waits for the kernel before it: every page but
+    // the one this CTA is about to write the new token into.
+    int next = p_begin, groups = 0;
     if (fuse.enabled) {
-        if (early) issue(p_begin, 0);
+        const int limit = writes_token ? p_end - 1 : p_end;
+        while (groups < NS - 1 && next < limit) { issue(next, (next - p_begin) % NS); ++next; ++groups; }
         pdl_wait();
     }
     // query fragments
@@ -221,10 +224,14 @@ attention_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict_
             fuse.v_cache_w[dst + j] = __float2bfloat16_rn(projected(row0, (H + KV + g) * HD + j));
         __syncthreads();                                 // the CTA's own copies below read these rows
     }
-    if (p_begin < p_end && !(fuse.enabled && early)) issue(p_begin, 0);
+    while (groups < NS - 1) {
+        if (next < p_end) { issue(next, (next - p_begin) % NS); ++next; } else cp_async_commit();
+        ++groups;
+    }
     for (int pi = p_begin; pi < p_end; ++pi) {
-        const int st = (pi - p_begin) & 1;
-        if (pi + 1 < p_end) { issue(pi + 1, st ^ 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
+        const int st = (pi - p_begin) % NS;
+        if (next < p_end) { issue(next, (next - p_begin) % NS); ++next; } else cp_async_commit();
+        cp_async_wait<NS - 1>();                         // all but the NS - 1 newest groups: page pi has landed
         __syncthreads();
         const bf16* ks_ = k_stage + st * PAGE * HD;
         const bf16* vs_ = v_stage + st * PAGE * HD;
@@ -418,7 +425,7 @@ __global__ void attention_mma_combine_kernel(const float* __restrict__ part_o, c
     }
 }
 
-template <int HD, int WM, int WN>
+template <int HD, int WM, int WN, int NS>
 static int launch_mma(const bf16* q, int q_stride, bf16* out, const bf16* k, const bf16* v, const int* table, int bps,
                       const int* cu, const int* slots, const int* starts, const int* news, float* po, float* pml,
                       int n_seqs, int max_new, int n_rows, int H, int KV, float scale, int window, int S,
@@ -431,14 +438,14 @@ static int launch_mma(const bf16* q, int q_stride, bf16* out, const bf16* k, con
     const int BT = ROWS / Gp;
     const dim3 grid((max_new + BT - 1) / BT, n_seqs, KV * S);
     if (grid.y > 65535 || grid.z > 65535) return KL_ERR_BAD_SIZE;
-    size_t smem = (size_t)4 * PAGE * HD * sizeof(bf16);
+    size_t smem = (size_t)2 * NS * PAGE * HD * sizeof(bf16);
     if (WN > 1) smem = max(smem, (size_t)(2 * WN * ROWS + WN * ROWS * HD) * sizeof(float));
     static bool configured = false;
     if (!configured) {
-        KL_CUDA(cudaFuncSetAttribute(attention_mma_kernel<HD, WM, WN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        KL_CUDA(cudaFuncSetAttribute(attention_mma_kernel<HD, WM, WN, NS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         configured = true;
     }
-    launch_kernel(attention_mma_kernel<HD, WM, WN>, grid, 32 * WM * WN, smem, stream, q, q_stride, out, k, v, table, bps, cu, slots,
+    launch_kernel(attention_mma_kernel<HD, WM, WN, NS>, grid, 32 * WM * WN, smem, stream, q, q_stride, out, k, v, table, bps, cu, slots,
         starts, news, po, pml, H, KV, Gp, scale * 1.4426950408889634f, window, S, fuse);
     KL_LAUNCH_CHECK();
     if (S > 1 && !fuse.enabled) {
@@ -466,12 +473,13 @@ static int attention_mma_dispatch(const void* q, int q_stride, void* out, const 
     if (KV <= 0 || H % KV || splits < 1) return KL_ERR_BAD_SIZE;
     if (splits > 1 && (part_o == nullptr || part_ml == nullptr)) return KL_ERR_BAD_SIZE;
     if (q_stride % 2 || ((uintptr_t)q & 3)) return KL_ERR_BAD_ALIGN;
-#define KL_MMA(HD, WM, WN)                                                                                            \
-    return launch_mma<HD, WM, WN>((const bf16*)q, q_stride, (bf16*)out, (const bf16*)k_cache, (const bf16*)v_cache,     \
+#define KL_MMA(HD, WM, WN, NS)                                                                                        \
+    return launch_mma<HD, WM, WN, NS>((const bf16*)q, q_stride, (bf16*)out, (const bf16*)k_cache, (const bf16*)v_cache,     \
                                   block_table, blocks_per_seq, cu_tokens, seq_slots, seq_starts, seq_new, part_o,      \
                                   part_ml, n_seqs, max_new, n_rows, H, KV, scale, window, splits, fuse, stream)
-    if (hd == 128) { if (few_rows) KL_MMA(128, 1, 4); else KL_MMA(128, 4, 1); }
-    if (hd == 64) { if (few_rows) KL_MMA(64, 1, 4); else KL_MMA(64, 4, 1); }
+    // two stages everywhere: a third one for decode (two CTAs per SM instead of three) measured slower
+    if (hd == 128) { if (few_rows) KL_MMA(128, 1, 4, 2); else KL_MMA(128, 4, 1, 2); }
+    if (hd == 64) { if (few_rows) KL_MMA(64, 1, 4, 2); else KL_MMA(64, 4, 1, 2); }
 #undef KL_MMA
     return KL_ERR_BAD_SIZE;
 }
