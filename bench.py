@@ -7,7 +7,8 @@ B200.
 A "step" is one decode step of a batch (default 8 sequences that each hold a 512-token
 prompt, context limit 4096).  One JSON line is printed:
 
-* ``value``     decoded tokens a second over K device-timed steps (CUDA events);
+* ``value``     decoded tokens a second over K device-timed steps (CUDA events); a step's token
+                ids stay on the device for the next step and are read on the host one step later;
 * ``e2e``       the same through the Python entry point ``LlamaInfer.generate`` with host
                 token lists in and out (every step copies its token ids to the device from
                 pinned memory and reads the sampled ids back);
@@ -140,21 +141,32 @@ def time_decode(infer, batch, steps, warmup, seed):
     g = torch.Generator().manual_seed(seed)
     vocab = infer.model.spec.vocab_size
     prompts = torch.randint(0, vocab, (batch, PROMPT_LEN), generator=g).tolist()
+    from kuiperllama_b200.engine.generate import _Tokens
     sampler = Sampler(SamplingParams())
     empty = torch.empty(0, dtype=torch.int32, device=eng.device)
+
+    def one_step(prev):
+        """Start the step that follows `prev` from its tokens on the device, then read `prev`'s
+        tokens on the host: the way the generation loop runs (one step ahead of the host)."""
+        nxt = _Tokens(sampler.sample(eng.decode_step(slots, prev.device_tokens), empty, empty))
+        prev.read()
+        return nxt
+
     with torch.inference_mode():
         slots = [eng.alloc_slot() for _ in range(batch)]
         logits = eng.step([SequenceInput(s, p, [len(p) - 1]) for s, p in zip(slots, prompts)])
-        tokens = sampler.sample(logits, empty, empty).tolist()
+        tokens = _Tokens(sampler.sample(logits, empty, empty))
         for _ in range(warmup):
-            tokens = sampler.sample(eng.decode_step(slots, tokens), empty, empty).tolist()
+            tokens = one_step(tokens)
+        tokens.read()
         torch.cuda.synchronize()
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         launches0 = ops.launch_count
         ctx0 = eng.cache.lengths[slots[0]]
         start.record()
         for _ in range(steps):
-            tokens = sampler.sample(eng.decode_step(slots, tokens), empty, empty).tolist()
+            tokens = one_step(tokens)
+        tokens.read()
         stop.record()
         torch.cuda.synchronize()
         seconds = start.elapsed_time(stop) / 1e3

@@ -29,10 +29,17 @@ from .step import Engine, SequenceInput
 
 
 class Backend(Protocol):
+    """What the loop needs of an engine.  ``prefill`` and ``decode`` return a *handle* to the
+    tokens they sampled (one per sequence, in the order given); ``read`` waits for a handle's
+    tokens and returns them as a list.  ``decode`` takes the handle of the step before and,
+    for each of its sequences, the place of that sequence's token in it, so a backend can run
+    a step before the host has seen the tokens that feed it."""
     def alloc_slot(self) -> int: ...
     def free_slot(self, slot: int) -> None: ...
-    def prefill(self, slots: List[int], prompts: List[Sequence[int]], request_ids: List[int]) -> List[int]: ...
-    def decode(self, slots: List[int], last_tokens: List[int], request_ids: List[int], steps: List[int]) -> List[int]: ...
+    def prefill(self, slots: List[int], prompts: List[Sequence[int]], request_ids: List[int]): ...
+    def decode(self, slots: List[int], previous, take: List[int], request_ids: List[int], steps: List[int]): ...
+    def read(self, handle) -> List[int]: ...
+    def select(self, handle, keep: List[int]): ...      # the handle of a subset, in the order of `keep`
 
 
 @dataclass
@@ -100,14 +107,34 @@ def run_requests(backend: Backend, prompts: Sequence[Sequence[int]], max_new_tok
         slots = [backend.alloc_slot() for _ in batch]
         t0 = time.perf_counter()
         new = backend.prefill(slots, [prompts[r] for r in batch], list(batch))
-        stats.prefill_seconds += time.perf_counter() - t0
         stats.prefill_tokens += sum(lens[r] for r in batch)
-        live: List[Tuple[int, int]] = list(zip(batch, slots))      # (request, slot)
+        live: List[Tuple[int, int]] = list(zip(batch, slots))      # (request, slot), in the order of `new`
         step = 0
+        t_decode = None
         while True:
-            still: List[Tuple[int, int]] = []
-            last: List[int] = []
-            for (r, slot), tok in zip(live, new):
+            # The next step is started before this step's tokens are read: it only needs them on
+            # the device.  A sequence that is certain to end with the token being read (its token
+            # limit or the cache's length limit) is left out; one that ends with a stop token has
+            # run one step for nothing, and that step's token for it is dropped.
+            ahead, take = [], []
+            for j, (r, slot) in enumerate(live):
+                made = len(results[r].tokens) + 1
+                if made < max_new_tokens and lens[r] + made < max_seq_len:
+                    ahead.append((r, slot))
+                    take.append(j)
+            nxt = None
+            if ahead:
+                step += 1
+                nxt = backend.decode([s for _, s in ahead], new, take, [r for r, _ in ahead], [step] * len(ahead))
+                stats.decode_steps += 1
+            tokens = backend.read(new)
+            if t_decode is None:
+                stats.prefill_seconds += time.perf_counter() - t0
+                t_decode = time.perf_counter()
+            else:
+                stats.decode_tokens += len(live)
+            finished = set()
+            for (r, slot), tok in zip(live, tokens):
                 res = results[r]
                 tok = int(tok)
                 if tok in stop:
@@ -121,19 +148,21 @@ def run_requests(backend: Backend, prompts: Sequence[Sequence[int]], max_new_tok
                     elif lens[r] + len(res.tokens) >= max_seq_len:
                         res.finish_reason = "context"    # the next token would not fit the cache
                 if res.finish_reason:
+                    finished.add(r)
                     backend.free_slot(slot)              # handed back at once; later batches reuse it
-                else:
-                    still.append((r, slot))
-                    last.append(tok)
-            live = still
-            if not live:
+            if nxt is None or all(r in finished for r, _ in ahead):
+                if nxt is not None:
+                    backend.read(nxt)                    # let the step that ran for nothing finish
                 break
-            step += 1
-            t0 = time.perf_counter()
-            new = backend.decode([s for _, s in live], last, [r for r, _ in live], [step] * len(live))
-            stats.decode_seconds += time.perf_counter() - t0
-            stats.decode_steps += 1
-            stats.decode_tokens += len(live)
+            if any(r in finished for r, _ in ahead):
+                # the step ahead ran for these too: go on with the others, from their places in it
+                keep = [j for j, (r, _) in enumerate(ahead) if r not in finished]
+                new = backend.select(nxt, keep)
+                live = [ahead[j] for j in keep]
+            else:
+                new, live = nxt, ahead
+        if t_decode is not None:
+            stats.decode_seconds += time.perf_counter() - t_decode
     return results
 
 
@@ -151,18 +180,43 @@ class EngineBackend:
     def free_slot(self, slot: int) -> None:
         self.engine.free_slot(slot)
 
-    def _sample(self, logits: torch.Tensor, request_ids: List[int], steps: List[int]) -> List[int]:
+    def _sample(self, logits: torch.Tensor, request_ids: List[int], steps: List[int]) -> "_Tokens":
         if self.sampler.greedy:
             ids = st = torch.empty(0, dtype=torch.int32, device=self.device)
         else:
             both = torch.tensor(request_ids + steps, dtype=torch.int32).to(self.device, non_blocking=True)
             ids, st = both[:len(request_ids)], both[len(request_ids):]
-        return self.sampler.sample(logits, ids, st).tolist()          # device -> host: the step's result
+        return _Tokens(self.sampler.sample(logits, ids, st))
 
     def prefill(self, slots, prompts, request_ids):
         logits = self.engine.step([SequenceInput(s, p, [len(p) - 1]) for s, p in zip(slots, prompts)])
         return self._sample(logits, list(request_ids), [0] * len(slots))
 
-    def decode(self, slots, last_tokens, request_ids, steps):
-        logits = self.engine.decode_step(slots, last_tokens)
+    def decode(self, slots, previous, take, request_ids, steps):
+        tokens = previous.device_tokens if take == list(range(previous.n)) else self.select(previous, take).device_tokens
+        logits = self.engine.decode_step(slots, tokens)
         return self._sample(logits, list(request_ids), list(steps))
+
+    def read(self, handle):
+        return handle.read()
+
+    def select(self, handle, keep):
+        idx = torch.tensor(keep, dtype=torch.int64).to(self.device, non_blocking=True)
+        return _Tokens(handle.device_tokens.index_select(0, idx))
+
+
+class _Tokens:
+    """Sampled tokens of one step: on the device for the step that follows, and on their way to
+    pinned host memory (the device-to-host read of the step's result) for the loop."""
+
+    def __init__(self, device_tokens: torch.Tensor):
+        self.device_tokens = device_tokens
+        self.n = device_tokens.numel()
+        self.host = torch.empty(self.n, dtype=torch.int32, pin_memory=True)
+        self.host.copy_(device_tokens, non_blocking=True)
+        self.event = torch.cuda.Event()
+        self.event.record()
+
+    def read(self) -> List[int]:
+        self.event.synchronize()
+        return self.host.tolist()

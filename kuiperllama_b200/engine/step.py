@@ -176,20 +176,25 @@ class Engine:
             return None
         return self.model.logits(residual, pending, want_rows)
 
-    def decode_step(self, slots: Sequence[int], tokens: Sequence[int]) -> torch.Tensor:
-        """One token for each of the given sequences; logits [len(slots), vocab].
+    def decode_step(self, slots: Sequence[int], tokens) -> torch.Tensor:
+        """One token for each of the given sequences; logits [len(slots), vocab].  ``tokens`` are
+        token ids on the host, or an int32 tensor on the device (the sampler's output of the step
+        before, which the host need not have seen yet).
 
         With ``use_graphs`` the step of a batch size is captured in a CUDA graph the first
         time it runs and replayed afterwards: the same kernels on the same buffers with one
         launch.  The logits tensor of a replayed step is the graph's own output buffer; it is
         overwritten by the next decode step of the same batch size."""
+        on_device = isinstance(tokens, torch.Tensor)
+        n = len(slots)
+        g = self._graphs.get(n) if self.use_graphs else None
+        if g is not None and self._staging is not None and g.staging_ptr == self._staging.dev.data_ptr():
+            return self._replay(g, list(slots), tokens if on_device else [int(t) for t in tokens])
+        if on_device:
+            tokens = tokens.tolist()                      # no graph for this size yet: the ordinary way, through the host
         if not self.use_graphs:
             return self.step([SequenceInput(s, [int(t)], [0]) for s, t in zip(slots, tokens)])
         from ..csrc import ops
-        n = len(slots)
-        g = self._graphs.get(n)
-        if g is not None and self._staging is not None and g.staging_ptr == self._staging.dev.data_ptr():
-            return self._replay(g, list(slots), [int(t) for t in tokens])
         inputs = [SequenceInput(s, [int(t)], [0]) for s, t in zip(slots, tokens)]
         ctx, want_rows, _ = self._pack(inputs, 0)
         if g is not None:                                 # the staging buffer moved: captured addresses are stale
@@ -217,15 +222,21 @@ class Engine:
             self.cache.lengths[s.slot] = st + 1
         return logits
 
-    def _replay(self, g: _DecodeGraph, slots: List[int], tokens: List[int]) -> torch.Tensor:
+    def _replay(self, g: _DecodeGraph, slots: List[int], tokens) -> torch.Tensor:
         """The short way through a decode step whose graph exists: the same checks and the same
-        staging layout as ``_pack`` for one token per sequence, then one graph launch."""
+        staging layout as ``_pack`` for one token per sequence, then one graph launch.  Token
+        ids that are already on the device are copied into place there (the embedding kernel
+        flags an id outside the vocabulary)."""
         from ..csrc import ops
         n = len(slots)
         cache, lengths = self.cache, self.cache.lengths
+        on_device = isinstance(tokens, torch.Tensor)
         if len(set(slots)) != n:
             raise StepError("a slot appears twice in one step")
-        if min(tokens) < 0 or max(tokens) >= self.model.spec.vocab_size:
+        if on_device:
+            if tokens.numel() != n or tokens.dtype != torch.int32 or not tokens.is_cuda:
+                raise StepError("device token ids must be an int32 CUDA tensor with one id per sequence")
+        elif min(tokens) < 0 or max(tokens) >= self.model.spec.vocab_size:
             raise StepError(f"a token id is outside the vocabulary of {self.model.spec.vocab_size}")
         starts = []
         for s in slots:
@@ -240,7 +251,10 @@ class Engine:
             starts.append(st)
         cache.flush_tables()
         # ids | positions | token_slot | slots | starts | news | cu | want
-        self._staging.upload(tokens + starts + slots + slots + starts + [1] * n + list(range(n + 1)) + list(range(n)))
+        ids = [0] * n if on_device else tokens
+        dev = self._staging.upload(ids + starts + slots + slots + starts + [1] * n + list(range(n + 1)) + list(range(n)))
+        if on_device:
+            dev[:n].copy_(tokens)
         g.graph.replay()
         ops.launch_count += g.launches
         for s, st in zip(slots, starts):

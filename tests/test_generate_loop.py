@@ -39,15 +39,23 @@ class FakeBackend:
             assert self.held[s] is None, "prefill into a slot that still holds a sequence"
             self.held[s] = list(p)
             out.append(self._next(self.held[s]))
-        return out
+        return out                                                   # a handle: here simply the list
 
-    def decode(self, slots, last_tokens, request_ids, steps):
+    def decode(self, slots, previous, take, request_ids, steps):
         self.log.append(("decode", tuple(request_ids), tuple(steps)))
         out = []
-        for s, t in zip(slots, last_tokens):
-            self.held[s].append(t)
+        for s, j in zip(slots, take):
+            assert s in self.held, "a step for a slot that was handed back"
+            self.held[s].append(previous[j])
             out.append(self._next(self.held[s]))
         return out
+
+    def read(self, handle):
+        self.log.append(("read", len(handle)))
+        return list(handle)
+
+    def select(self, handle, keep):
+        return [handle[j] for j in keep]
 
 
 def expected(prompt, max_new, stop=()):
@@ -73,7 +81,7 @@ def test_batches_follow_one_another_and_every_slot_comes_back():
     assert [e[1] for e in prefills] == [(0, 1, 2, 3), (4, 5, 6, 7), (8, 9, 10)]
     assert set(prefills[1][2]) == set(prefills[0][2])              # the second batch reuses the slots
     assert stats.prefill_tokens == sum(len(p) for p in prompts)
-    assert stats.decode_tokens == 11 * 5
+    assert stats.decode_tokens == 11 * 5 and stats.decode_steps == 3 * 5   # no step runs for nothing without stop tokens
 
 
 def test_stop_tokens_end_a_sequence_early_and_are_left_out():
@@ -86,13 +94,16 @@ def test_stop_tokens_end_a_sequence_early_and_are_left_out():
         assert r.tokens == want and r.finish_reason == why
     assert res[1].tokens == [] and res[1].finish_reason == "stop"  # stopped at its first token
     assert not be.held
-    # the finished sequences left the batch: later decode steps carry fewer requests
+    # A step is started before the tokens that feed it are read, so a sequence that meets a stop
+    # token has run one more step for nothing; after that it is gone: batches only shrink.
     sizes = [len(e[1]) for e in be.log if e[0] == "decode"]
-    assert sizes[0] < 4 and sizes == sorted(sizes, reverse=True)
-    # its slot came back before the others went on
+    assert sizes[0] == 4 and sizes[1] < 4 and sizes == sorted(sizes, reverse=True)
+    order = [e[0] for e in be.log]
+    assert order[:3] == ["prefill", "decode", "read"]                  # one step ahead of the host
+    # the stopped sequence's slot comes back as soon as its token has been read
     first_free = next(i for i, e in enumerate(be.log) if e[0] == "free")
-    first_decode = next(i for i, e in enumerate(be.log) if e[0] == "decode")
-    assert first_free < first_decode
+    second_decode = [i for i, e in enumerate(be.log) if e[0] == "decode"][1]
+    assert first_free < second_decode
     with_stop = run_requests(FakeBackend(8), prompts, max_new_tokens=9, stop_ids=stop, include_stop=True)
     assert with_stop[1].tokens == [FakeBackend._next([10, 11])]
 

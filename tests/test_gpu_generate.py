@@ -106,7 +106,7 @@ def test_temperature_sampling_follows_the_counter_draw(model_folders, dtype):
         class Shift:
             def __getattr__(self, k): return getattr(be, k)
             def prefill(self, s, p, ids): return be.prefill(s, p, [2])
-            def decode(self, s, t, ids, st): return be.decode(s, t, [2], st)
+            def decode(self, s, prev, take, ids, st): return be.decode(s, prev, take, [2], st)
         with torch.inference_mode():
             alone = run_requests(Shift(), [prompts[2]], 12)
         assert alone[0].tokens == out[2]
