@@ -153,28 +153,80 @@ attention_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict_
     // query fragments
     uint32_t qa[KS][4];
     const int width = (H + 2 * KV) * HD;
-    auto projected = [&](int token_row, int idx) {       // element idx of a token's q|k|v row, float32
-        if (fuse.n_partials == 0) return to_f32(fuse.qkv[(size_t)token_row * width + idx]);
-        const float* p = fuse.partials + (size_t)token_row * width + idx;
-        float a = 0.f;
-        for (int zz = 0; zz < fuse.n_partials; ++zz) a += p[(size_t)zz * fuse.partial_stride];
-        return a;
-    };
     if (fuse.enabled) {
-        // q = sum of the pieces, rotated, built once per CTA in shared memory (one pair per thread
-        // and turn), then picked up as fragments.  All valid rows are heads of the sequence's one token.
+        // The token's q (this group's heads), and in the CTA whose pages end at the token also its k
+        // and v, are made here: the sum of the product's pieces, rotated.  Work is cut into items of
+        // four neighbouring elements (and their four rotation partners), one per thread and turn, and
+        // an item's loads are all requested before any is used: the CTA waits for memory once.
         __shared__ __align__(16) bf16 q_sm[16 * HD];
-        const int tpos = start + t0;
-        for (int idx = threadIdx.x; idx < G * (HD / 2); idx += THREADS) {
-            const int hh = idx / (HD / 2), j = idx % (HD / 2);
-            const int base = (g * G + hh) * HD;
-            const float x = projected(row0 + t0, base + j), y = projected(row0 + t0, base + j + HD / 2);
-            float sn, cs;
-            sincosf((float)tpos * fuse.inv_freq[j], &sn, &cs);
-            q_sm[hh * HD + j] = __float2bfloat16_rn(x * cs - y * sn);
-            q_sm[hh * HD + j + HD / 2] = __float2bfloat16_rn(y * cs + x * sn);
+        constexpr int QI = HD / 8;                       // items per head: HD / 2 pairs, four at a time
+        const int n_q = G * QI, n_k = writes_token ? QI : 0, n_v = writes_token ? HD / 4 : 0;
+        const size_t dst = writes_token ? (((size_t)table[max_pos / PAGE] * KV + g) * PAGE + (max_pos % PAGE)) * HD : 0;
+        for (int item = threadIdx.x; item < n_q + n_k + n_v; item += THREADS) {
+            const bool is_q = item < n_q, is_k = !is_q && item < n_q + n_k;
+            const int hh = is_q ? item / QI : 0;
+            const int j = is_q ? (item % QI) * 4 : (is_k ? (item - n_q) * 4 : (item - n_q - n_k) * 4);
+            const int col = is_q ? (g * G + hh) * HD + j : (is_k ? (H + g) * HD + j : (H + KV + g) * HD + j);
+            const size_t off = (size_t)(is_q ? row0 + t0 : row0) * width + col;
+            const bool rot = is_q || is_k;
+            float4 x = make_float4(0.f, 0.f, 0.f, 0.f), y = x;
+            if (fuse.n_partials == 0) {
+                const uint2 rx = *reinterpret_cast<const uint2*>(fuse.qkv + off);
+                const float2 x01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&rx.x));
+                const float2 x23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&rx.y));
+                x = make_float4(x01.x, x01.y, x23.x, x23.y);
+                if (rot) {
+                    const uint2 ry = *reinterpret_cast<const uint2*>(fuse.qkv + off + HD / 2);
+                    const float2 y01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ry.x));
+                    const float2 y23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ry.y));
+                    y = make_float4(y01.x, y01.y, y23.x, y23.y);
+                }
+            } else {
+                for (int z0 = 0; z0 < fuse.n_partials; z0 += 8) {      // pieces are added in ascending order
+                    float4 px[8], py[8];
+#pragma unroll
+                    for (int zz = 0; zz < 8; ++zz) {
+                        const float* p = fuse.partials + (size_t)(z0 + zz) * fuse.partial_stride + off;
+                        const bool in = z0 + zz < fuse.n_partials;
+                        px[zz] = in ? __ldcg(reinterpret_cast<const float4*>(p)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                        py[zz] = (in && rot) ? __ldcg(reinterpret_cast<const float4*>(p + HD / 2)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
+#pragma unroll
+                    for (int zz = 0; zz < 8; ++zz) {
+                        x.x += px[zz].x; x.y += px[zz].y; x.z += px[zz].z; x.w += px[zz].w;
+                        y.x += py[zz].x; y.y += py[zz].y; y.z += py[zz].z; y.w += py[zz].w;
+                    }
+                }
+            }
+            uint2 lo_half, hi_half;                      // elements j..j+3 and their partners j + HD / 2 ..
+            if (rot) {
+                const float4 f = *reinterpret_cast<const float4*>(fuse.inv_freq + j);
+                const float angle = (float)(is_q ? start + t0 : max_pos);
+                float sn[4], cs[4];
+                sincosf(angle * f.x, &sn[0], &cs[0]);
+                sincosf(angle * f.y, &sn[1], &cs[1]);
+                sincosf(angle * f.z, &sn[2], &cs[2]);
+                sincosf(angle * f.w, &sn[3], &cs[3]);
+                lo_half.x = pack_bf16(x.x * cs[0] - y.x * sn[0], x.y * cs[1] - y.y * sn[1]);
+                lo_half.y = pack_bf16(x.z * cs[2] - y.z * sn[2], x.w * cs[3] - y.w * sn[3]);
+                hi_half.x = pack_bf16(y.x * cs[0] + x.x * sn[0], y.y * cs[1] + x.y * sn[1]);
+                hi_half.y = pack_bf16(y.z * cs[2] + x.z * sn[2], y.w * cs[3] + x.w * sn[3]);
+            } else {
+                lo_half.x = pack_bf16(x.x, x.y);
+                lo_half.y = pack_bf16(x.z, x.w);
+                hi_half = lo_half;
+            }
+            if (is_q) {
+                *reinterpret_cast<uint2*>(q_sm + hh * HD + j) = lo_half;
+                *reinterpret_cast<uint2*>(q_sm + hh * HD + j + HD / 2) = hi_half;
+            } else if (is_k) {
+                *reinterpret_cast<uint2*>(fuse.k_cache_w + dst + j) = lo_half;
+                *reinterpret_cast<uint2*>(fuse.k_cache_w + dst + j + HD / 2) = hi_half;
+            } else {
+                *reinterpret_cast<uint2*>(fuse.v_cache_w + dst + j) = lo_half;
+            }
         }
-        __syncthreads();
+        __syncthreads();                                 // q_sm is whole; the CTA's own copies below read the new cache rows
 #pragma unroll
         for (int ks = 0; ks < KS; ++ks) {
 #pragma unroll
@@ -209,21 +261,6 @@ attention_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict_
     for (int n = 0; n < ON; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 
-    if (writes_token) {
-        // this CTA's pages end at the new token: put its rotated key and its value into the cache
-        // first (the token is row0 of the sequence; position max_pos), then read the page as usual
-        const size_t dst = (((size_t)table[max_pos / PAGE] * KV + g) * PAGE + (max_pos % PAGE)) * HD;
-        for (int j = threadIdx.x; j < HD / 2; j += THREADS) {
-            const float x = projected(row0, (H + g) * HD + j), y = projected(row0, (H + g) * HD + j + HD / 2);
-            float sn, cs;
-            sincosf((float)max_pos * fuse.inv_freq[j], &sn, &cs);
-            fuse.k_cache_w[dst + j] = __float2bfloat16_rn(x * cs - y * sn);
-            fuse.k_cache_w[dst + j + HD / 2] = __float2bfloat16_rn(y * cs + x * sn);
-        }
-        for (int j = threadIdx.x; j < HD; j += THREADS)
-            fuse.v_cache_w[dst + j] = __float2bfloat16_rn(projected(row0, (H + KV + g) * HD + j));
-        __syncthreads();                                 // the CTA's own copies below read these rows
-    }
     while (groups < NS - 1) {
         if (next < p_end) { issue(next, (next - p_begin) % NS); ++next; } else cp_async_commit();
         ++groups;
@@ -319,40 +356,45 @@ attention_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict_
     }
     if constexpr (WN > 1) {
         // merge the warps that shared the rows: through shared memory (the stages are free now)
+        constexpr int OS = HD + 8;                                   // row stride of sm_o: rows 8 banks apart
         float* sm_m = reinterpret_cast<float*>(smem_raw);            // [WN][ROWS]
         float* sm_l = sm_m + WN * ROWS;                              // [WN][ROWS]
-        float* sm_o = sm_l + WN * ROWS;                              // [WN][ROWS][HD]
+        float* sm_o = sm_l + WN * ROWS;                              // [WN][ROWS][OS]
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
+            if (!valid[i]) continue;                                 // rows of padding are never read
             const int r = warp_m * 16 + quad + 8 * i;
             if (tq == 0) { sm_m[warp_n * ROWS + r] = m[i]; sm_l[warp_n * ROWS + r] = l[i]; }
 #pragma unroll
-            for (int n = 0; n < ON; ++n) {
-                sm_o[((size_t)warp_n * ROWS + r) * HD + n * 8 + 2 * tq] = o[n][2 * i];
-                sm_o[((size_t)warp_n * ROWS + r) * HD + n * 8 + 2 * tq + 1] = o[n][2 * i + 1];
-            }
+            for (int n = 0; n < ON; ++n)
+                *reinterpret_cast<float2*>(sm_o + ((size_t)warp_n * ROWS + r) * OS + n * 8 + 2 * tq) = make_float2(o[n][2 * i], o[n][2 * i + 1]);
         }
         __syncthreads();
-        for (int idx = threadIdx.x; idx < ROWS * HD; idx += THREADS) {
-            const int r = idx / HD, d = idx % HD;
+        const int n_rows = min(BT, T - t0) * Gp;                     // rows of the tile that belong to tokens
+        for (int item = threadIdx.x; item < n_rows * (HD / 4); item += THREADS) {
+            const int r = item / (HD / 4), d = (item % (HD / 4)) * 4;
             const int tl = t0 + r / Gp, hh = r % Gp;
-            if (tl >= T || hh >= G) continue;
+            if (hh >= G) continue;
             float M = -INFINITY;
 #pragma unroll
             for (int w = 0; w < WN; ++w) M = fmaxf(M, sm_m[w * ROWS + r]);
-            float L = 0.f, acc = 0.f;
+            float L = 0.f;
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
             for (int w = 0; w < WN; ++w) {
                 const float mw = sm_m[w * ROWS + r];
                 const float c = mw == -INFINITY ? 0.f : exp2f(mw - M);
                 L += sm_l[w * ROWS + r] * c;
-                acc += sm_o[((size_t)w * ROWS + r) * HD + d] * c;
+                const float4 v = *reinterpret_cast<const float4*>(sm_o + ((size_t)w * ROWS + r) * OS + d);
+                acc.x += v.x * c; acc.y += v.y * c; acc.z += v.z * c; acc.w += v.w * c;
             }
             const size_t orow = (size_t)(row0 + tl) * H + (g * G + hh);
-            if (S == 1) out[orow * HD + d] = __float2bfloat16_rn(acc / L);
-            else {
-                part_o[(orow * S + z) * HD + d] = acc;
-                if (d == 0) { part_ml[(orow * S + z) * 2] = M; part_ml[(orow * S + z) * 2 + 1] = L; }
+            if (S == 1) {
+                const float inv = 1.f / L;
+                *reinterpret_cast<uint2*>(out + orow * HD + d) = make_uint2(pack_bf16(acc.x * inv, acc.y * inv), pack_bf16(acc.z * inv, acc.w * inv));
+            } else {
+                *reinterpret_cast<float4*>(part_o + (orow * S + z) * HD + d) = acc;
+                if (d == 0) *reinterpret_cast<float2*>(part_ml + (orow * S + z) * 2) = make_float2(M, L);
             }
         }
         if (fuse.enabled && S > 1) {
@@ -368,19 +410,37 @@ attention_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict_
             __syncthreads();
             if (is_last) {
                 __threadfence();
-                for (int idx = threadIdx.x; idx < G * HD; idx += THREADS) {
-                    const int hh = idx / HD, d = idx % HD;
+                // four output elements per thread and turn; eight pieces are requested at a time and merged
+                // into a running maximum, sum and output, in ascending order
+                for (int item = threadIdx.x; item < G * (HD / 4); item += THREADS) {
+                    const int hh = item / (HD / 4), d = (item % (HD / 4)) * 4;
                     const size_t orow = (size_t)row0 * H + (g * G + hh);
-                    float M = -INFINITY;
-                    for (int zz = 0; zz < S; ++zz) M = fmaxf(M, __ldcg(&part_ml[(orow * S + zz) * 2]));
-                    float L = 0.f, acc = 0.f;
-                    for (int zz = 0; zz < S; ++zz) {
-                        const float mz = __ldcg(&part_ml[(orow * S + zz) * 2]);
-                        const float c = mz == -INFINITY ? 0.f : exp2f(mz - M);
-                        L += __ldcg(&part_ml[(orow * S + zz) * 2 + 1]) * c;
-                        acc += __ldcg(&part_o[(orow * S + zz) * HD + d]) * c;
+                    float M = -INFINITY, L = 0.f;
+                    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                    for (int z0 = 0; z0 < S; z0 += 8) {
+                        float2 ml[8];
+                        float4 po[8];
+#pragma unroll
+                        for (int zz = 0; zz < 8; ++zz) {
+                            const bool in = z0 + zz < S;
+                            ml[zz] = in ? __ldcg(reinterpret_cast<const float2*>(part_ml + (orow * S + z0 + zz) * 2)) : make_float2(-INFINITY, 0.f);
+                            po[zz] = in ? __ldcg(reinterpret_cast<const float4*>(part_o + (orow * S + z0 + zz) * HD + d)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                        }
+                        float Mc = M;
+#pragma unroll
+                        for (int zz = 0; zz < 8; ++zz) Mc = fmaxf(Mc, ml[zz].x);
+                        const float keep = M == -INFINITY ? 0.f : exp2f(M - Mc);     // Mc is finite when M is
+                        L *= keep; acc.x *= keep; acc.y *= keep; acc.z *= keep; acc.w *= keep;
+#pragma unroll
+                        for (int zz = 0; zz < 8; ++zz) {
+                            const float c = ml[zz].x == -INFINITY ? 0.f : exp2f(ml[zz].x - Mc);
+                            L += ml[zz].y * c;
+                            acc.x += po[zz].x * c; acc.y += po[zz].y * c; acc.z += po[zz].z * c; acc.w += po[zz].w * c;
+                        }
+                        M = Mc;
                     }
-                    out[orow * HD + d] = __float2bfloat16_rn(acc / L);
+                    const float inv = 1.f / L;
+                    *reinterpret_cast<uint2*>(out + orow * HD + d) = make_uint2(pack_bf16(acc.x * inv, acc.y * inv), pack_bf16(acc.z * inv, acc.w * inv));
                 }
             }
         }
@@ -439,7 +499,7 @@ static int launch_mma(const bf16* q, int q_stride, bf16* out, const bf16* k, con
     const dim3 grid((max_new + BT - 1) / BT, n_seqs, KV * S);
     if (grid.y > 65535 || grid.z > 65535) return KL_ERR_BAD_SIZE;
     size_t smem = (size_t)2 * NS * PAGE * HD * sizeof(bf16);
-    if (WN > 1) smem = max(smem, (size_t)(2 * WN * ROWS + WN * ROWS * HD) * sizeof(float));
+    if (WN > 1) smem = max(smem, (size_t)(2 * WN * ROWS + WN * ROWS * (HD + 8)) * sizeof(float));
     static bool configured = false;
     if (!configured) {
         KL_CUDA(cudaFuncSetAttribute(attention_mma_kernel<HD, WM, WN, NS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));

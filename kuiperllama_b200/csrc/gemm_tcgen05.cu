@@ -46,6 +46,17 @@ struct GemmArgs {
     int tiles_n;        //   blockIdx.x walks them in groups of TC_GROUP_M token tiles (see tile_of)
     int swiglu;         // 1: the B (or A) operand's rows alternate 64 gate rows and 64 up rows; the
                         //    epilogue writes silu(gate) * up, half as many output features, bf16
+    // Weights-as-rows only, for the few tokens of a decode step (see "the residual stream inside
+    // the products" below).
+    const float* scale_ss;    // every token's result is multiplied by rsqrt(sum / K + scale_eps), the sum
+    int scale_ss_n;           //   given in pieces [scale_ss_n][64] by the product before (the 1 / rms of a
+    float scale_eps;          //   norm whose weight is already in the activations)
+    int K;
+    float* sink;              // the split's partial sums are added into this residual stream [rows_b, rows_a]
+    float* sink_ss;           //   by the last CTA of each row tile, which also leaves sum(x^2) of its
+    int* sink_counters;       //   128 columns per row in sink_ss[tile][64]; counters are zero between launches
+    const float* sink_w;      // with sink: the next norm's weight [rows_a], and where bf16(x * w) of the new
+    __nv_bfloat16* sink_scaled;   //   rows goes [rows_b, rows_a] (the next product's activations); may be null
 };
 
 // Tile order for tokens-as-rows: all the feature tiles of a group of TC_GROUP_M token tiles
@@ -64,7 +75,7 @@ __device__ __forceinline__ void tile_of(int id, int tiles_m, int tiles_n, int& t
 __device__ __forceinline__ float silu_mul(float g, float u) { return g * (1.0f / (1.0f + __expf(-g))) * u; }
 
 template <int BN, int STAGES, bool WEIGHT_ROWS>
-__global__ void __launch_bounds__(TC_THREADS, 1)
+__global__ void __launch_bounds__(TC_THREADS, WEIGHT_ROWS ? 2 : 1)      // weights-as-rows: two CTAs share an SM
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmArgs args) {
     constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2, B_BYTES = BN * TC_BK * 2;
     constexpr uint32_t ACC_COLS = BN < 32 ? 32 : BN;      // columns of one accumulator
@@ -183,6 +194,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         // ---------------------------------------------------------------- epilogue: warps 2..5
         const int quarter = warp & 3;                         // the 32 tensor-memory lanes this warp may read
         pdl_wait();                                           // before this grid writes anything
+        __shared__ float inv_rms[64];                         // weights-as-rows: the factor of every token (column)
+        if constexpr (WEIGHT_ROWS) {
+            const int et = threadIdx.x - 64;                  // 0..127 among the epilogue threads
+            if (et < 64) {
+                float f = 1.0f;
+                if (args.scale_ss != nullptr) {
+                    float ss = 0.f;
+                    if (et < args.rows_b)
+                        for (int j = 0; j < args.scale_ss_n; ++j) ss += args.scale_ss[j * 64 + et];
+                    f = rsqrtf(ss / (float)args.K + args.scale_eps);
+                }
+                inv_rms[et] = f;
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+        }
         int lt = 0;
         for (int t = blockIdx.x; t < n_tiles; t += gridDim.x, ++lt) {
         int tile_a, tile_b;
@@ -209,7 +235,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                             for (int j = 0; j < 16; ++j) r[j] = 0u;
                         }
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) xch[(c + j) * 64 + f] = __uint_as_float(r[j]);
+                        for (int j = 0; j < 16; ++j) xch[(c + j) * 64 + f] = __uint_as_float(r[j]) * inv_rms[c + j];
                     }
                 }
                 asm volatile("bar.sync 1, 128;" ::: "memory");             // the four epilogue warps, whatever happened
@@ -229,7 +255,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                                 const int m = c + j;
                                 if (m < args.rows_b)
                                     outb[(size_t)m * args.ld_out + feature] =
-                                        __float2bfloat16_rn(silu_mul(__uint_as_float(r[j]), xch[m * 64 + f]));
+                                        __float2bfloat16_rn(silu_mul(__uint_as_float(r[j]) * inv_rms[m], xch[m * 64 + f]));
                             }
                         }
                     }
@@ -251,11 +277,69 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         for (int j = 0; j < 16; ++j) {
                             const int m = c + j;
                             if (m < args.rows_b) {
-                                if (args.out_f32) out[(size_t)m * args.ld_out + row] = __uint_as_float(r[j]);
-                                else outb[(size_t)m * args.ld_out + row] = __float2bfloat16_rn(__uint_as_float(r[j]));
+                                const float v = __uint_as_float(r[j]) * inv_rms[m];
+                                if (args.out_f32) out[(size_t)m * args.ld_out + row] = v;
+                                else outb[(size_t)m * args.ld_out + row] = __float2bfloat16_rn(v);
                             }
                         }
                     }
+                }
+            }
+            if (args.sink != nullptr) {
+                // The last CTA of this row tile (over the k cuts) adds all pieces, in ascending order, into
+                // the residual stream and leaves the sum of squares of its 128 columns for every row.
+                __shared__ int last_flag;
+                __shared__ float ss_part[4][64];
+                __threadfence();
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (threadIdx.x == 64) {
+                    const int done = atomicAdd(&args.sink_counters[tile_a], 1);
+                    last_flag = done == (int)gridDim.z - 1;
+                    if (last_flag) args.sink_counters[tile_a] = 0;
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (last_flag) {
+                    __threadfence();
+                    // Four rows at a time and four pieces at a time, so that 16 loads are in flight per
+                    // thread; every sum still runs over the pieces in ascending order.
+                    const float* part = (const float*)args.out + row;
+                    float* stream = args.sink + row;
+                    const bool live = row < args.rows_a;
+                    const int Z = (int)gridDim.z;
+                    const float nw = (live && args.sink_scaled != nullptr) ? args.sink_w[row] : 0.f;
+                    for (int m0 = 0; m0 < args.rows_b; m0 += 4) {
+                        float x[4];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            x[j] = (live && m0 + j < args.rows_b) ? stream[(size_t)(m0 + j) * args.rows_a] : 0.f;
+                        for (int z0 = 0; z0 < Z; z0 += 4) {
+                            float p[4][4];
+#pragma unroll
+                            for (int zz = 0; zz < 4; ++zz)
+#pragma unroll
+                                for (int j = 0; j < 4; ++j)
+                                    p[zz][j] = (live && z0 + zz < Z && m0 + j < args.rows_b)
+                                        ? __ldcg(part + (size_t)(z0 + zz) * args.split_stride + (size_t)(m0 + j) * args.ld_out) : 0.f;
+#pragma unroll
+                            for (int zz = 0; zz < 4; ++zz)
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) x[j] += p[zz][j];
+                        }
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            if (live && m0 + j < args.rows_b) {
+                                stream[(size_t)(m0 + j) * args.rows_a] = x[j];
+                                if (args.sink_scaled != nullptr)
+                                    args.sink_scaled[(size_t)(m0 + j) * args.rows_a + row] = __float2bfloat16_rn(x[j] * nw);
+                            }
+                            const float sq = warp_sum(x[j] * x[j]);
+                            if (lane == 0 && m0 + j < 64) ss_part[quarter][m0 + j] = sq;
+                        }
+                    }
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    const int et = threadIdx.x - 64;
+                    if (et < args.rows_b)
+                        args.sink_ss[tile_a * 64 + et] = (ss_part[0][et] + ss_part[1][et]) + (ss_part[2][et] + ss_part[3][et]);
                 }
             }
         } else if (ok) {
@@ -413,13 +497,26 @@ KL_API int kl_gemm_tcgen05(const void* a, long long lda, const void* w, long lon
 // Few tokens (M <= 64): weights as tile rows, the K range cut into `splits` pieces.
 // splits == 1: out[M, N] directly (bf16 or float32).  splits > 1: out is float32
 // [splits, M, N] partial sums (out_f32 must be 1) for the caller to add.
+//
+// The residual stream inside the products (decode steps).  With `sink` (float32 [M, N]; out must be
+// the float32 pieces, any splits >= 1) the last CTA of every 128-column tile adds the pieces into
+// `sink` in ascending order, writes the tile's sum of squares per row to sink_ss[tile][64] and, with
+// `sink_scaled` (bf16 [M, N]), the new rows times `sink_w` [N] (the weight of the norm that follows);
+// `sink_counters` (int32 [tiles]) are zero before and after.  With `scale_ss` (float32
+// [scale_ss_n][64], pieces of every token's sum of squares) every token's result is multiplied by
+// rsqrt(sum / K + scale_eps): with activations x * w this is the product of the normalised rows,
+// norm(x) = w * x / rms(x).  Together they remove the add-and-normalise kernel between two products.
 KL_API int kl_gemm_tcgen05_skinny(const void* a, long long lda, const void* w, long long ldw, void* out, long long ldo,
-                                  int M, int N, int K, int splits, int out_f32, int swiglu, int* status,
-                                  cudaStream_t stream) {
+                                  int M, int N, int K, int splits, int out_f32, int swiglu, const float* scale_ss,
+                                  int scale_ss_n, float scale_eps, float* sink, float* sink_ss, int* sink_counters,
+                                  const float* sink_w, void* sink_scaled, int* status, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return KL_OK;
     if (M > 64) return KL_ERR_BAD_SIZE;
     if (swiglu && (splits != 1 || out_f32 || N % 128)) return KL_ERR_BAD_SIZE;
-    if (!aligned_operand(a, lda, K) || !aligned_operand(w, ldw, K)) return KL_ERR_BAD_ALIGN;
+    if (!aligned_operand(w, ldw, K) || !aligned_operand(a, lda, K)) return KL_ERR_BAD_ALIGN;
+    if (scale_ss != nullptr && scale_ss_n < 1) return KL_ERR_BAD_SIZE;
+    if (sink != nullptr && (!out_f32 || swiglu || sink_ss == nullptr || sink_counters == nullptr || ldo != N ||
+                            (sink_scaled != nullptr && sink_w == nullptr))) return KL_ERR_BAD_SIZE;
     const int k_blocks = (K + TC_BK - 1) / TC_BK;
     if (splits < 1 || splits > k_blocks || splits > 65535) return KL_ERR_BAD_SIZE;
     if (splits > 1 && !out_f32) return KL_ERR_BAD_DTYPE;
@@ -428,7 +525,8 @@ KL_API int kl_gemm_tcgen05_skinny(const void* a, long long lda, const void* w, l
     int rc;
     if ((rc = make_map(&ma, w, N, K, ldw, TC_BM)) != KL_OK) return rc;
     if ((rc = make_map(&mb, a, M, K, lda, bn)) != KL_OK) return rc;
-    GemmArgs args{out, ldo, (long long)M * ldo, N, M, k_blocks, out_f32, status, 0, 0, swiglu};
+    GemmArgs args{out, ldo, (long long)M * ldo, N, M, k_blocks, out_f32, status, 0, 0, swiglu,
+                  scale_ss, scale_ss_n, scale_eps, K, sink, sink_ss, sink_counters, sink_w, (__nv_bfloat16*)sink_scaled};
     dim3 grid((N + TC_BM - 1) / TC_BM, 1, splits);
     // two CTAs share an SM so that one's epilogue overlaps the other's loads
     if (bn == 16) return launch<16, 6, true>(ma, mb, args, grid, stream);

@@ -315,6 +315,81 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bo
                                                _ptr(status_word(a.device)), _stream()), "gemm_tcgen05")
 
 
+# arguments of kl_gemm_tcgen05_skinny that switch the residual-stream forms off
+_NO_STREAM_FUSION = (ctypes.c_void_p(0), 0, ctypes.c_float(0.0), ctypes.c_void_p(0), ctypes.c_void_p(0), ctypes.c_void_p(0),
+                     ctypes.c_void_p(0), ctypes.c_void_p(0))
+
+STREAM_FUSION_MAX_ROWS = 64
+STREAM_SINK_MAX_ROWS = 16       # more rows: the last CTA's pass over the pieces costs more than a kernel of its own
+
+
+def stream_fusable(rows: int, w: torch.Tensor) -> bool:
+    """Whether a product of ``rows`` tokens with ``w`` can add its result into the float32 residual
+    stream, or apply a norm's 1 / rms to its rows, inside the kernel (decode steps, bfloat16)."""
+    return (rows <= STREAM_FUSION_MAX_ROWS and w.dtype == torch.bfloat16 and w.is_cuda and w.shape[1] % 8 == 0
+            and w.stride(1) == 1 and w.stride(0) % 8 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemm_skinny_stream(w: torch.Tensor, a: torch.Tensor, row_scale=None, sink=None, swiglu: bool = False,
+                       splits: Optional[int] = None):
+    """A decode step's product with the residual stream folded in (see gemm_tcgen05.cu).
+
+    ``a``: bfloat16 [M, K].  ``row_scale`` = (ss float32 [pieces, 64], eps): row m of the result is
+    multiplied by rsqrt(sum_p ss[p, m] / K + eps); with a = bf16(x * norm_weight) that is the
+    product of the normalised rows of x.
+    Result: with ``sink`` = (stream float32 [M, N], next norm's weight float32 [N] or None) the
+    product is added into the stream and (ss float32 [N / 128 tiles, 64], bf16(stream * weight)
+    [M, N] or None) comes back; with ``swiglu`` a bfloat16 [M, N / 2] tensor; else float32 pieces
+    [S, M, N]."""
+    N, K = w.shape
+    M = a.shape[0]
+    _cuda(a, w)
+    _need(a.dtype == torch.bfloat16 and a.shape[1] == K and a.stride(1) == 1 and a.stride(0) % 8 == 0
+          and a.data_ptr() % 16 == 0, "gemm_skinny_stream: activations")
+    _need(stream_fusable(M, w), "gemm_skinny_stream: shape or layout not supported")
+    if row_scale is not None:
+        ss, eps = row_scale
+        _cuda(ss)
+        _need(ss.dtype == torch.float32 and ss.is_contiguous() and ss.dim() == 2 and ss.shape[1] == 64,
+              "gemm_skinny_stream: sums of squares")
+        scale_args = (_ptr(ss), ss.shape[0], ctypes.c_float(eps))
+    else:
+        scale_args = (ctypes.c_void_p(0), 0, ctypes.c_float(0.0))
+    dev = w.device
+    L = lib("gemm_tcgen05")
+    st = _ptr(status_word(dev))
+    null = ctypes.c_void_p(0)
+    if swiglu:
+        _need(sink is None and N % 128 == 0, "gemm_skinny_stream: swiglu")
+        out = torch.empty((M, N // 2), dtype=torch.bfloat16, device=dev)
+        _check(L.kl_gemm_tcgen05_skinny(_ptr(a), ctypes.c_longlong(a.stride(0)), _ptr(w), ctypes.c_longlong(w.stride(0)), _ptr(out),
+                                        ctypes.c_longlong(out.stride(0)), M, N, K, 1, 0, 1, *scale_args, null, null, null, null,
+                                        null, st, _stream()), "gemm_skinny_stream")
+        return out
+    splits = skinny_splits(N, K) if splits is None else splits
+    partial = torch.empty((splits, M, N), dtype=torch.float32, device=dev)
+    result = partial
+    sink_args = (null, null, null, null, null)
+    if sink is not None:
+        stream, next_w = sink
+        _cuda(stream)
+        _need(stream.dtype == torch.float32 and stream.is_contiguous() and tuple(stream.shape) == (M, N), "gemm_skinny_stream: sink")
+        tiles = (N + 127) // 128
+        ss_out = torch.empty((tiles, 64), dtype=torch.float32, device=dev)
+        scaled = None
+        if next_w is not None:
+            _cuda(next_w)
+            _need(next_w.dtype == torch.float32 and next_w.is_contiguous() and next_w.numel() == N, "gemm_skinny_stream: norm weight")
+            scaled = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+        sink_args = (_ptr(stream), _ptr(ss_out), _ptr(_zero_counters(dev, tiles, "gemm")),
+                     _ptr(next_w) if next_w is not None else null, _ptr(scaled) if scaled is not None else null)
+        result = (ss_out, scaled)
+    _check(L.kl_gemm_tcgen05_skinny(_ptr(a), ctypes.c_longlong(a.stride(0)), _ptr(w), ctypes.c_longlong(w.stride(0)), _ptr(partial),
+                                    ctypes.c_longlong(N), M, N, K, splits, 1, 0, *scale_args, *sink_args, st, _stream()),
+           "gemm_skinny_stream")
+    return result
+
+
 def gemm_skinny_partials(a: torch.Tensor, w: torch.Tensor, splits: Optional[int] = None) -> Optional[torch.Tensor]:
     """The pieces of a @ w^T for M <= 64 tokens as float32 [S, M, N], for a consumer that adds
     them itself (the norm after a projection, the rotary kernel after q/k/v); None when the
@@ -331,7 +406,8 @@ def gemm_skinny_partials(a: torch.Tensor, w: torch.Tensor, splits: Optional[int]
     partial = torch.empty((splits, M, N), dtype=torch.float32, device=a.device)
     _check(lib("gemm_tcgen05").kl_gemm_tcgen05_skinny(
         _ptr(a), ctypes.c_longlong(a.stride(0)), _ptr(w), ctypes.c_longlong(w.stride(0)), _ptr(partial),
-        ctypes.c_longlong(N), M, N, K, splits, 1, 0, _ptr(status_word(a.device)), _stream()), "gemm_skinny")
+        ctypes.c_longlong(N), M, N, K, splits, 1, 0, *_NO_STREAM_FUSION, _ptr(status_word(a.device)), _stream()),
+        "gemm_skinny")
     return partial
 
 
@@ -352,11 +428,13 @@ def gemm_skinny(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, splits: Opt
     if splits == 1:
         _check(L.kl_gemm_tcgen05_skinny(_ptr(a), ctypes.c_longlong(a.stride(0)), _ptr(w), ctypes.c_longlong(w.stride(0)),
                                         _ptr(out), ctypes.c_longlong(out.stride(0)), M, N, K, 1,
-                                        int(out.dtype == torch.float32), int(swiglu), st, _stream()), "gemm_skinny")
+                                        int(out.dtype == torch.float32), int(swiglu), *_NO_STREAM_FUSION, st, _stream()),
+               "gemm_skinny")
         return
     partial = torch.empty((splits, M, N), dtype=torch.float32, device=a.device)
     _check(L.kl_gemm_tcgen05_skinny(_ptr(a), ctypes.c_longlong(a.stride(0)), _ptr(w), ctypes.c_longlong(w.stride(0)),
-                                    _ptr(partial), ctypes.c_longlong(N), M, N, K, splits, 1, 0, st, _stream()), "gemm_skinny")
+                                    _ptr(partial), ctypes.c_longlong(N), M, N, K, splits, 1, 0, *_NO_STREAM_FUSION, st,
+                                    _stream()), "gemm_skinny")
     _check(L.kl_splitk_reduce(_ptr(partial), splits, M, N, _ptr(out), ctypes.c_longlong(out.stride(0)),
                               int(out.dtype == torch.float32), _stream()), "splitk_reduce")
 
@@ -489,12 +567,13 @@ def attention_tcgen05(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache
 # Which kernel prefill steps of the bfloat16 path use for head size 128: "tcgen05" or "mma".
 PREFILL_KERNEL = "tcgen05"
 
-_counters: Dict[int, torch.Tensor] = {}
+_counters: Dict[tuple, torch.Tensor] = {}
 
 
-def _zero_counters(device: torch.device, n: int) -> torch.Tensor:
-    """int32 counters that kernels leave at zero (the last CTA of a group resets its own)."""
-    idx = device.index if device.index is not None else torch.cuda.current_device()
+def _zero_counters(device: torch.device, n: int, use: str = "attention") -> torch.Tensor:
+    """int32 counters that kernels leave at zero (the last CTA of a group resets its own); one
+    buffer per device and per use, so that kernels of different kinds never share a counter."""
+    idx = (device.index if device.index is not None else torch.cuda.current_device(), use)
     have = _counters.get(idx)
     if have is None or have.numel() < n:
         have = torch.zeros(max(n, 1 << 16), dtype=torch.int32, device=device)
@@ -530,6 +609,7 @@ def attention_decode_fused(qkv: torch.Tensor, inv_freq: torch.Tensor, out: torch
     _need(k_cache.is_contiguous() and v_cache.is_contiguous() and k_cache.dtype == torch.bfloat16
           and tuple(k_cache.shape[1:]) == (num_kv_heads, PAGE, head_dim), "attention_decode_fused: cache layout")
     _need(inv_freq.dtype == torch.float32 and inv_freq.numel() == head_dim // 2, "attention_decode_fused: inv_freq")
+    _need(all(t.data_ptr() % 16 == 0 for t in (qkv, inv_freq, out, k_cache, v_cache)), "attention_decode_fused: 16-byte aligned operands")
     if splits is None:
         ctas = max(1, n * num_kv_heads)
         splits = max(1, min(16, (2 * SM_COUNT + ctas - 1) // ctas))

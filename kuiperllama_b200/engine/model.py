@@ -56,6 +56,9 @@ class DecoderModel:
         else:
             self.lm_head = Linear(tensors[spec.lm_head_name], runtime)
         self.error_flag = torch.zeros(1, dtype=torch.int32, device=dev)
+        # In decode steps of the bfloat16 path a block may let its products add into the residual
+        # stream themselves and finish the norms in their epilogues (see parts/block.py).
+        self.stream_fusion = dt == torch.bfloat16
 
     def _build_layer(self, layer: LayerSpec, tensors):
         rt = self.runtime
@@ -90,14 +93,19 @@ class DecoderModel:
     def hidden_states(self, step: StepContext, cache: SequenceCache) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
         """Run embedding and all scheduled layers: the float32 residual stream and the last
         feed-forward's output that is still to be added to it."""
+        step.allow_stream_fusion = self.stream_fusion and step.is_decode
         residual = torch.empty((step.n_tokens, self.spec.hidden_size), dtype=torch.float32, device=self.runtime.device)
         ops.embedding(step.token_ids[:step.n_tokens], self.embedding, residual, self.error_flag)
         first = self.blocks[self.spec.schedule[0].layer]
         if getattr(first, "position", None) is not None:
             first.position.add_to_embeddings(residual, step)
         pending = None
-        for i, entry in enumerate(self.spec.schedule):
+        schedule = self.spec.schedule
+        for i, entry in enumerate(schedule):
+            following = self.blocks[schedule[i + 1].layer] if i + 1 < len(schedule) else None
+            step.next_norm = getattr(following, "mixer_norm", None) if following is not None else self.final_norm
             residual, pending = self.blocks[entry.layer].forward(residual, pending, step, cache.view(i))
+        step.next_norm = None
         return residual, pending
 
     def logits(self, residual: torch.Tensor, pending: Optional[torch.Tensor], rows: torch.Tensor) -> torch.Tensor:

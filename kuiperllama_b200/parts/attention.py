@@ -28,6 +28,9 @@ class AttentionMixer(Mixer):
     projections are stacked into one matrix at load so that one product makes q, k and v.
     """
 
+    accepts_lazy_norm = True      # the q/k/v product can normalise the stream's rows itself
+    may_accumulate = True         # the output product can add into the stream itself
+
     @classmethod
     def manifest(cls, spec: PartSpec, prefix: str) -> Dict[str, TensorDecl]:
         hid, H, KV, hd = spec["hidden_size"], spec["num_heads"], spec["num_kv_heads"], spec["head_dim"]
@@ -66,7 +69,7 @@ class AttentionMixer(Mixer):
             attn = torch.empty((n, self.H * self.hd), dtype=self.runtime.dtype, device=x.device)
             ops.attention_decode_fused(qkv, self.inv_freq, attn, cache.k, cache.v, cache.block_table, step, self.H, self.KV,
                                        self.hd, self.scale, int(self.window or 0))
-            return self.o.forward(attn, allow_partials=True)
+            return self.o.forward(attn, allow_partials=True, sink=step.residual_sink)
         parts = None
         if qkv.dim() == 3:                                         # pieces of the product: the rotary kernel adds them
             parts, qkv = qkv, torch.empty(qkv.shape[1:], dtype=self.runtime.dtype, device=x.device)
@@ -76,4 +79,4 @@ class AttentionMixer(Mixer):
         attn = torch.empty((n, self.H * self.hd), dtype=self.runtime.dtype, device=x.device)
         ops.attention(qkv, qkv.shape[1], attn, cache.k, cache.v, cache.block_table, step, self.H, self.KV, self.hd,
                       self.scale, int(self.window or 0))
-        return self.o.forward(attn, allow_partials=True)
+        return self.o.forward(attn, allow_partials=True, sink=step.residual_sink)

@@ -52,6 +52,61 @@ class StepContext:
     host_slots: List[int]         # host copies for parts that plan their launches
     host_starts: List[int]
     host_new: List[int]
+    # Set by the block around a call of a mixer or feed-forward that says it ``may_accumulate``:
+    # the float32 residual stream its result is to be added to, with the norm that will read the
+    # stream next.  Such a part may add the result itself (inside its last product) and return
+    # ``Accumulated`` instead of a tensor.
+    residual_sink: Optional["StreamSink"] = None
+    # Set by the model before a block runs: the norm that will receive the block's pending result
+    # (the next scheduled block's first norm, or the final norm), and whether this step may fold
+    # the residual stream into the products at all.
+    next_norm: Optional["Norm"] = None
+    allow_stream_fusion: bool = False
+
+
+@dataclass
+class StreamSink:
+    residual: torch.Tensor        # float32 [n_tokens, hidden], updated in place
+    norm: "Norm"                  # the norm that reads it next; it has ``weight`` (float32 [hidden]) and ``eps``
+
+
+@dataclass
+class Accumulated:
+    """A part's result that is already in the residual stream.  ``ss`` holds, in pieces
+    [pieces, 64], the sum of squares of every row of the stream after the addition, and
+    ``scaled`` the new rows times the weight of ``norm`` in the compute dtype: together what
+    that norm needs to hand normalised rows on without a pass of its own."""
+    ss: torch.Tensor
+    scaled: torch.Tensor
+    norm: "Norm"
+
+
+@dataclass
+class NormedLazy:
+    """Rows that a norm has not finished: y = scaled * rsqrt(sum(x^2) / width + eps), with
+    ``scaled`` = weight * x in the compute dtype and sum(x^2) known in pieces.  A product of few
+    tokens multiplies by the factor in its epilogue (it is one number per row, so it commutes
+    with the product); everything else calls ``dense()``."""
+    residual: torch.Tensor
+    weight: torch.Tensor
+    eps: float
+    ss: torch.Tensor
+    scaled: torch.Tensor
+    dtype: torch.dtype
+
+    @property
+    def shape(self):
+        return self.residual.shape
+
+    @property
+    def device(self):
+        return self.residual.device
+
+    def dense(self) -> torch.Tensor:
+        from ..csrc import ops
+        out = torch.empty(self.residual.shape, dtype=self.dtype, device=self.residual.device)
+        ops.add_rmsnorm(self.residual, None, self.weight, out, self.eps)
+        return out
 
 
 class Part:
@@ -72,7 +127,12 @@ class Norm(Part):
     """``forward(residual, delta, n_rows, rows)``: adds ``delta`` (None, [n, hidden] in the
     compute dtype, or float32 partial sums [S, n, hidden]) to the float32 residual stream in
     place and returns the normalised rows in the compute dtype.  With ``rows`` only those rows
-    are produced and the residual is left unchanged."""
+    are produced and the residual is left unchanged.
+
+    A norm that sets ``accepts_accumulated`` also takes ``Accumulated`` as delta (the sum is in
+    the stream already) and may then return ``NormedLazy`` for the part that follows."""
+
+    accepts_accumulated = False
 
     def forward(self, residual: torch.Tensor, delta: Optional[torch.Tensor], n_rows: int,
                 rows: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -99,6 +159,11 @@ class Mixer(Part):
     float32 partial sums [S, n_tokens, hidden] whose sum over S is that result; the norm
     that follows adds them in ascending order."""
 
+    # A part that sets these takes ``NormedLazy`` as input, and may add its result into
+    # ``step.residual_sink`` itself and return ``Accumulated``.
+    accepts_lazy_norm = False
+    may_accumulate = False
+
     def __init__(self, spec, prefix, tensors, runtime, position: Optional[PositionEncoding] = None):
         super().__init__(spec, prefix, tensors, runtime)
         self.position = position
@@ -116,6 +181,9 @@ class Mixer(Part):
 class FeedForward(Part):
     """``forward(x, step)``: [n_tokens, hidden] -> [n_tokens, hidden], token by token (or
     float32 partial sums [S, n_tokens, hidden], as a mixer may)."""
+
+    accepts_lazy_norm = False
+    may_accumulate = False
 
     def forward(self, x: torch.Tensor, step: StepContext) -> torch.Tensor:
         raise NotImplementedError

@@ -6,7 +6,7 @@ from typing import Optional, Tuple
 import torch
 
 from ..cache import CacheView
-from .base import FeedForward, Mixer, Norm, StepContext, register_arrangement
+from .base import FeedForward, Mixer, Norm, NormedLazy, StepContext, StreamSink, register_arrangement
 
 
 @register_arrangement("pre_norm")
@@ -23,9 +23,25 @@ class PreNormBlock:
         self.mixer_norm, self.mixer = mixer_norm, mixer
         self.feed_forward_norm, self.feed_forward = feed_forward_norm, feed_forward
 
-    def forward(self, residual: torch.Tensor, pending: Optional[torch.Tensor], step: StepContext,
-                cache: CacheView) -> Tuple[torch.Tensor, torch.Tensor]:
+    def forward(self, residual: torch.Tensor, pending, step: StepContext, cache: CacheView):
+        # Where the step allows it (decode), a part that can add into the stream itself is given
+        # the stream, and a part that can normalise the stream's rows itself is given them lazily.
+        fuse = step.allow_stream_fusion
+        after = step.next_norm                       # the norm that receives this block's pending result
+
+        def sink_for(part, norm):
+            ok = fuse and part.may_accumulate and norm is not None and getattr(norm, "accepts_accumulated", False)
+            return StreamSink(residual, norm) if ok else None
+
         n = self.mixer_norm.forward(residual, pending, step.n_tokens)
+        if isinstance(n, NormedLazy) and not self.mixer.accepts_lazy_norm:
+            n = n.dense()
+        step.residual_sink = sink_for(self.mixer, self.feed_forward_norm)
         mixed = self.mixer.forward(n, step, cache)
         n = self.feed_forward_norm.forward(residual, mixed, step.n_tokens)
-        return residual, self.feed_forward.forward(n, step)
+        if isinstance(n, NormedLazy) and not self.feed_forward.accepts_lazy_norm:
+            n = n.dense()
+        step.residual_sink = sink_for(self.feed_forward, after)
+        out = self.feed_forward.forward(n, step)
+        step.residual_sink = None
+        return residual, out

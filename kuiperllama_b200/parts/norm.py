@@ -8,7 +8,7 @@ import torch
 from ..config.spec import PartSpec
 from ..csrc import ops
 from ..weights.loader import TensorDecl
-from .base import Norm, Runtime, register_norm
+from .base import Accumulated, Norm, NormedLazy, Runtime, register_norm
 
 
 @register_norm("rmsnorm")
@@ -27,8 +27,15 @@ class RMSNorm(Norm):
         self.eps = float(spec["eps"])
         self.weight = tensors[prefix + spec["name"]].to(device=runtime.device, dtype=torch.float32).contiguous()
 
-    def forward(self, residual: torch.Tensor, delta: Optional[torch.Tensor], n_rows: int,
-                rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    accepts_accumulated = True
+
+    def forward(self, residual: torch.Tensor, delta, n_rows: int, rows: Optional[torch.Tensor] = None):
+        if isinstance(delta, Accumulated):
+            # the stream holds the sum already; if the rows times this norm's weight came with it,
+            # the product that follows only has to apply 1 / rms
+            if rows is None and delta.norm is self and delta.scaled is not None:
+                return NormedLazy(residual, self.weight, self.eps, delta.ss, delta.scaled, self.runtime.dtype)
+            delta = None
         n_out = rows.numel() if rows is not None else residual.shape[0]
         out = torch.empty((n_out, self.size), dtype=self.runtime.dtype, device=residual.device)
         ops.add_rmsnorm(residual, delta, self.weight, out, self.eps, rows)

@@ -8,7 +8,7 @@ import torch
 from ..config.spec import PartSpec
 from ..csrc import ops
 from ..weights.loader import TensorDecl
-from .base import FeedForward, Runtime, StepContext, register_feed_forward
+from .base import FeedForward, NormedLazy, Runtime, StepContext, register_feed_forward
 from .linear import Linear
 
 
@@ -19,6 +19,9 @@ class SwiGLUFeedForward(FeedForward):
     gate = w1, up = w3, down = w2, tools/export_llama3.py:583-585).  Gate and up are stacked
     into one matrix at load (and the activation is applied in that product's epilogue where the
     tensor-core kernel runs).  Spec: ``hidden_size``, ``intermediate_size``, ``names``."""
+
+    accepts_lazy_norm = True
+    may_accumulate = True
 
     @classmethod
     def manifest(cls, spec: PartSpec, prefix: str) -> Dict[str, TensorDecl]:
@@ -39,10 +42,16 @@ class SwiGLUFeedForward(FeedForward):
         del gate, up
         self.down = Linear(tensors[prefix + n["down"]], runtime)
 
-    def forward(self, x: torch.Tensor, step: StepContext) -> torch.Tensor:
+    def forward(self, x, step: StepContext):
+        if isinstance(x, NormedLazy):
+            if self.fused and ops.stream_fusable(x.shape[0], self.gate_up.weight):
+                # gate, up and the activation in one kernel that also finishes the norm before them
+                act = ops.gemm_skinny_stream(self.gate_up.weight, x.scaled, row_scale=(x.ss, x.eps), swiglu=True)
+                return self.down.forward(act, allow_partials=True, sink=getattr(step, "residual_sink", None))
+            x = x.dense()
         act = torch.empty((x.shape[0], self.inter), dtype=self.runtime.dtype, device=x.device)
         if self.fused:
             ops.matmul_swiglu(x, self.gate_up.weight, act)
         else:
             ops.swiglu(self.gate_up.forward(x), act)
-        return self.down.forward(act, allow_partials=True)
+        return self.down.forward(act, allow_partials=True, sink=getattr(step, "residual_sink", None))

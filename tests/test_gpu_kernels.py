@@ -638,3 +638,64 @@ def test_attention_tcgen05_finds_one_far_key_among_thousands(ops):
         for j in range(new):
             if far <= n - new + j:
                 _close(out[j].view(H, hd), want, "bfloat16", f"far key at {far}, query {j}")
+
+
+@pytest.mark.parametrize("M,N,K,splits", [(1, 128, 64, 1), (8, 4096, 4096, None), (16, 1000, 520, 3), (33, 384, 136, 2),
+                                          (64, 640, 1024, 4), (5, 4096, 14336, None)])
+def test_products_with_the_residual_stream_folded_in(ops, M, N, K, splits):
+    """The two decode forms of the skinny product.  Consumer: activations are the stream's rows
+    times the norm weight, and the epilogue multiplies row m by rsqrt(mean(x_m^2) + eps) from
+    pieces of sum(x^2): the product of the normalised rows.  Producer: the result is added into a
+    residual stream by the last CTA of every column tile, which also returns the pieces of the
+    new rows' sums of squares and the new rows times the next norm's weight.  Twice, to show the
+    counters are left at zero."""
+    torch.manual_seed(23)
+    eps = 1e-5
+    w = (torch.randn(N, K, device=DEV) * 0.05).bfloat16()
+    for round_ in range(2):
+        x = torch.randn(M, K, device=DEV) * 2
+        nw = 1 + 0.1 * torch.randn(K, device=DEV)
+        pieces = 3
+        ss = torch.zeros(pieces, 64, device=DEV)
+        full = (x * x).sum(1)
+        ss[0, :M] = full * 0.25
+        ss[1, :M] = full * 0.5
+        ss[2, :M] = full - ss[0, :M] - ss[1, :M]
+        scaled = (x * nw).bfloat16()
+        inv = torch.rsqrt((x.double() ** 2).mean(1) + eps).cpu()
+        ref = (scaled.double().cpu() * inv[:, None]) @ w.double().cpu().T
+        # the same thing is the product of the normalised rows, up to the rounding of the rows
+        normed = plain_llama.rmsnorm(x.cpu(), nw.cpu(), eps).double() @ w.double().cpu().T
+        assert float((ref - normed).abs().max()) <= 1e-2 * float(normed.abs().max())
+        got = ops.gemm_skinny_stream(w, scaled, row_scale=(ss, eps), splits=splits)
+        ops.check_status(torch.device(DEV))
+        err = float((got.sum(0).double().cpu() - ref).abs().max())
+        assert err <= 1e-4 * float(ref.abs().max()) + 1e-5, f"product with 1 / rms in the epilogue {M}x{N}x{K}: {err:.3e}"
+        # the same product added into a stream
+        a = (scaled.float() * inv.float().to(DEV)[:, None]).bfloat16()
+        ref_a = a.double().cpu() @ w.double().cpu().T
+        sink = torch.randn(M, N, device=DEV)
+        next_w = 1 + 0.1 * torch.randn(N, device=DEV)
+        before = sink.clone()
+        ss_out, scaled_out = ops.gemm_skinny_stream(w, a, sink=(sink, next_w), splits=splits)
+        ops.check_status(torch.device(DEV))
+        want = before.double().cpu() + ref_a
+        err = float((sink.double().cpu() - want).abs().max())
+        assert err <= 1e-4 * float(ref_a.abs().max()) + 1e-5, f"product added into the stream {M}x{N}x{K}: {err:.3e}"
+        got_ss = ss_out[:, :M].sum(0).double().cpu()
+        want_ss = (sink.double().cpu() ** 2).sum(1)
+        assert float(((got_ss - want_ss) / want_ss).abs().max()) < 1e-5, "sums of squares of the new rows"
+        assert torch.equal(scaled_out, (sink * next_w).bfloat16()), "the new rows times the next norm's weight"
+        only_ss, none = ops.gemm_skinny_stream(w, a, sink=(before.clone(), None), splits=splits)
+        assert none is None and torch.equal(only_ss[:, :M], ss_out[:, :M])
+    if N % 128 == 0 and K % 8 == 0:
+        gate = (torch.randn(N // 2, K, device=DEV) * 0.05).bfloat16()
+        up = (torch.randn(N // 2, K, device=DEV) * 0.05).bfloat16()
+        if (N // 2) % 64 == 0:
+            act = ops.gemm_skinny_stream(ops.interleave_gate_up(gate, up), scaled, row_scale=(ss, eps), swiglu=True)
+            rows = scaled.double().cpu() * inv[:, None]
+            g = rows @ gate.double().cpu().T
+            u = rows @ up.double().cpu().T
+            r = g / (1 + torch.exp(-g)) * u
+            assert float((act.double().cpu() - r).abs().max()) <= 8e-3 * float(r.abs().max()) + 1e-6
+    assert int(ops._zero_counters(torch.device(DEV), 1, "gemm").abs().sum()) == 0
