@@ -320,7 +320,7 @@ _NO_STREAM_FUSION = (ctypes.c_void_p(0), 0, ctypes.c_float(0.0), ctypes.c_void_p
                      ctypes.c_void_p(0), ctypes.c_void_p(0))
 
 STREAM_FUSION_MAX_ROWS = 64
-STREAM_SINK_MAX_ROWS = 16       # more rows: the last CTA's pass over the pieces costs more than a kernel of its own
+STREAM_SINK_MAX_ROWS = 4        # measured on the 8B shape: faster than a norm kernel of its own up to 4 rows, slower from 8
 
 
 def stream_fusable(rows: int, w: torch.Tensor) -> bool:
