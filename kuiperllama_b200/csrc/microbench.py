@@ -5,6 +5,7 @@ repeats, a buffer larger than L2 written between repeats), and print the achieve
     python -m kuiperllama_b200.csrc.microbench gemm_tcgen05 --m 2048 --n 6144 --k 4096
     python -m kuiperllama_b200.csrc.microbench attention_prefill --tokens 2048 --heads 32 --kv-heads 8 --head-dim 128 [--mma]
     python -m kuiperllama_b200.csrc.microbench attention_decode --batch 64 --context 640 --heads 32 --kv-heads 8 --head-dim 128
+    python -m kuiperllama_b200.csrc.microbench attention_decode --batch 8 --context 516 --fused     (the decode step's form)
 
 It is also the small case that profiler captures of single kernels are taken on.
 """
@@ -67,6 +68,8 @@ def main(argv=None) -> int:
     ap.add_argument("--repeats", type=int, default=20)
     ap.add_argument("--simt", action="store_true", help="attention_decode: the split-KV SIMT kernel instead of the tensor-core one")
     ap.add_argument("--mma", action="store_true", help="attention_prefill: the mma.sync kernel instead of the tcgen05 one")
+    ap.add_argument("--fused", action="store_true", help="attention_decode: the form of a decode step (sums six pieces of "
+                    "the q/k/v product, rotates, writes the token into the cache, attends, merges the splits)")
     args = ap.parse_args(argv)
     torch.manual_seed(0)
     out = {"kernel": args.kernel}
@@ -108,7 +111,14 @@ def main(argv=None) -> int:
             pos, slots = i32([N - 1] * B), i32(list(range(B)))
             cu, st, nw = i32(list(range(B + 1))), i32([N - 1] * B), i32([1] * B)
             splits = args.splits or max(1, min(16, (2 * ops.SM_COUNT + B * KV - 1) // (B * KV)))
-            if args.simt:
+            if args.fused:
+                from types import SimpleNamespace
+                step = SimpleNamespace(n_seqs=B, n_tokens=B, is_decode=True, cu_tokens=cu, seq_slots=slots, seq_starts=st, seq_new=nw)
+                pieces = torch.randn(6, B, (H + 2 * KV) * hd, device=DEV)
+                inv_freq = (500000.0 ** (-torch.arange(0, hd, 2, dtype=torch.float64) / hd)).float().to(DEV)
+                splits = args.splits
+                fn = lambda: ops.attention_decode_fused(pieces, inv_freq, o, k, v, table, step, H, KV, hd, scale, 0, args.splits)
+            elif args.simt:
                 fn = lambda: ops.attention_decode(q, q.shape[1], o, k, v, table, pos, slots, B, H, KV, hd, scale, 0, args.splits)
             else:
                 fn = lambda: ops.attention_mma(q, q.shape[1], o, k, v, table, cu, slots, st, nw, B, 1, B, H, KV, hd, scale, 0, splits, True)
