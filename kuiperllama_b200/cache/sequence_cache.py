@@ -7,6 +7,10 @@ execution of a layer that asks for them, and fixed-size state per slot.
   are equal (kind, kv heads, head size, window) form a *group*; each group has storage, a
   page pool and a block table of its own, so layers with different needs do not share a
   layout.  The storage of one execution is ``[pages, kv_heads, PAGE, head_dim]``.
+* A group whose mixers read only a *window* of the most recent keys holds only the pages that
+  the window still touches: before a step, the pages of a sequence that lie wholly below
+  ``length - window + 1`` go back to the group's pool (no query of this or a later step reads
+  them), so such a group can be given a smaller pool (``window_step_tokens``).
 * Beside the pages every execution may ask for per-slot state of a fixed shape (a
   recurrent mixer's state, for instance).  It is zeroed when a slot is handed out.  The
   dense Llama decoder asks for none.
@@ -28,8 +32,9 @@ PAGE = 64      # tokens per page; the kernels are compiled for the same number
 
 @dataclass(frozen=True)
 class KVRequest:
-    """Token-indexed storage a mixer asks for.  ``kind`` "full": every key is kept.
-    ``window`` is the number of most recent keys the mixer reads (None: all)."""
+    """Token-indexed storage a mixer asks for.  ``kind`` "full": keys are stored by position.
+    ``window`` is the number of most recent keys the mixer reads (None: all); with a window
+    the pages that no query can reach any more are given back while the sequence grows."""
     kv_heads: int
     head_dim: int
     kind: str = "full"
@@ -70,8 +75,14 @@ class _Group:
         # is still queued on the device.
         self.table_host = torch.zeros((n_slots, blocks_per_seq), dtype=torch.int32)
         self.table = torch.zeros((n_slots, blocks_per_seq), dtype=torch.int32, device=device)
+        # a sequence's pages by block index; a block below the window that was given back is -1
         self.slot_pages: List[List[int]] = [[] for _ in range(n_slots)]
+        self.first_block: List[int] = [0] * n_slots            # blocks below this one were given back
         self.dirty: set = set()
+
+    def pages_of(self, slot: int) -> List[int]:
+        """The pages the sequence in ``slot`` holds now."""
+        return [p for p in self.slot_pages[slot] if p >= 0]
 
 
 class SequenceCache:
@@ -79,11 +90,15 @@ class SequenceCache:
     sequence's count rounded up to a multiple of ``PAGE``; it sizes every group's pool.
     ``max_seq_len`` bounds one sequence.  ``kv_requests[i]`` / ``state_requests[i]`` are the
     requests of schedule entry i (None: nothing); ``cache_from[i]`` names an earlier entry
-    whose storage entry i reads instead of owning some."""
+    whose storage entry i reads instead of owning some.  ``window_step_tokens``: the most tokens
+    a sequence brings in one step, if the caller can promise one; the pool of a group with a
+    window is then sized for ``window + window_step_tokens`` tokens per slot instead of for
+    ``max_tokens``."""
 
     def __init__(self, kv_requests: Sequence[Optional[KVRequest]],
                  state_requests: Sequence[Optional[StateRequest]], cache_from: Sequence[Optional[int]],
-                 max_tokens: int, max_seq_len: int, dtype: torch.dtype, device, max_slots: Optional[int] = None):
+                 max_tokens: int, max_seq_len: int, dtype: torch.dtype, device, max_slots: Optional[int] = None,
+                 window_step_tokens: Optional[int] = None):
         if max_tokens < PAGE:
             raise CacheError(f"max_tokens {max_tokens} is less than one page of {PAGE} tokens")
         self.device = torch.device(device)
@@ -101,8 +116,16 @@ class SequenceCache:
         for i, (req, src) in enumerate(zip(kv_requests, cache_from)):
             if req is not None and src is None:
                 by_request.setdefault(req, []).append(i)
+        def pool_size(req: KVRequest) -> int:
+            if req.window is None or window_step_tokens is None:
+                return self.n_pages
+            # the window's keys and the step's new tokens, both possibly straddling page borders
+            per_slot = pages_for(req.window + window_step_tokens, PAGE) + 1
+            return max(1, min(self.n_pages, self.n_slots * per_slot))
+
+        self.window_step_tokens = window_step_tokens
         self.groups: List[_Group] = [
-            _Group(req, entries, self.n_pages, self.n_slots, self.blocks_per_seq, dtype, self.device)
+            _Group(req, entries, pool_size(req), self.n_slots, self.blocks_per_seq, dtype, self.device)
             for req, entries in by_request.items()]
         self._where: Dict[int, Tuple[_Group, int]] = {}
         for g in self.groups:
@@ -132,21 +155,33 @@ class SequenceCache:
         if not self.slots.is_held(slot):
             raise CacheError(f"slot {slot} is freed but is not held")
         for g in self.groups:
-            for p in reversed(g.slot_pages[slot]):
+            for p in reversed(g.pages_of(slot)):
                 g.pages.give_back(p)
             g.slot_pages[slot] = []
+            g.first_block[slot] = 0
         self.lengths[slot] = 0
         self.slots.give_back(slot)
 
     def reserve(self, slot: int, new_length: int) -> None:
-        """Make room for the sequence in ``slot`` to hold ``new_length`` tokens."""
+        """Make room for the sequence in ``slot`` to hold ``new_length`` tokens; called before
+        the step that brings the tokens beyond ``lengths[slot]``."""
         if not self.slots.is_held(slot):
             raise CacheError(f"slot {slot} is not held")
         if new_length > self.max_seq_len:
             raise CacheError(f"a sequence of {new_length} tokens exceeds the cache's limit of {self.max_seq_len}")
+        if self.window_step_tokens is not None and new_length - self.lengths[slot] > self.window_step_tokens:
+            raise CacheError(f"a step of {new_length - self.lengths[slot]} tokens exceeds the promised {self.window_step_tokens}")
         need = pages_for(new_length, PAGE)
         for g in self.groups:
             have = g.slot_pages[slot]
+            if g.request.window is not None:
+                # the first key any query of this step (positions lengths[slot] and up) or of a later
+                # one reads is lengths[slot] - window + 1: whole blocks below it go back to the pool
+                keep_from = min(max(0, self.lengths[slot] - g.request.window + 1) // PAGE, len(have))
+                for b in range(g.first_block[slot], keep_from):
+                    g.pages.give_back(have[b])
+                    have[b] = -1
+                g.first_block[slot] = max(g.first_block[slot], keep_from)
             if need > len(have):
                 fresh = g.pages.take_many(need - len(have))
                 for p in fresh:
@@ -180,6 +215,9 @@ class SequenceCache:
 
     def pages_held(self) -> List[int]:
         return [g.pages.held() for g in self.groups]
+
+    def pool_sizes(self) -> List[int]:
+        return [g.pages.n for g in self.groups]
 
     def bytes(self) -> int:
         n = sum(g.k.numel() * g.k.element_size() * 2 for g in self.groups)

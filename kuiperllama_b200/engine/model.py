@@ -83,11 +83,13 @@ class DecoderModel:
             src.append(e.cache_from)
         return kv, st, src
 
-    def new_cache(self, max_tokens: int, max_seq_len: Optional[int] = None, max_slots: Optional[int] = None) -> SequenceCache:
+    def new_cache(self, max_tokens: int, max_seq_len: Optional[int] = None, max_slots: Optional[int] = None,
+                  window_step_tokens: Optional[int] = None) -> SequenceCache:
         kv, st, src = self.cache_requests()
         return SequenceCache(kv, st, src, max_tokens=max_tokens,
                              max_seq_len=max_seq_len or self.spec.max_positions,
-                             dtype=self.runtime.dtype, device=self.runtime.device, max_slots=max_slots)
+                             dtype=self.runtime.dtype, device=self.runtime.device, max_slots=max_slots,
+                             window_step_tokens=window_step_tokens)
 
     # ------------------------------------------------------------------ forward
     def hidden_states(self, step: StepContext, cache: SequenceCache) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:

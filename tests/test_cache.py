@@ -102,7 +102,7 @@ def test_random_traffic_never_loses_or_doubles_anything():
             c.free_slot(s)
             del live[s]
         g = c.groups[0]
-        held = [p for s in live for p in g.slot_pages[s]]
+        held = [p for s in live for p in g.pages_of(s)]
         assert len(held) == len(set(held)) == g.pages.held()
         assert all(len(g.slot_pages[s]) == pages_for(live[s], PAGE) for s in live)
         assert c.slots.held() == len(live)
@@ -140,3 +140,59 @@ def test_reading_another_entrys_cache_and_state():
     with pytest.raises(CacheError):
         SequenceCache([None, KVRequest(2, 16)], [None, None], [None, 0], max_tokens=PAGE, max_seq_len=PAGE,
                       dtype=torch.float32, device="cpu")
+
+
+def test_a_group_with_a_window_gives_back_the_pages_below_it():
+    """Two groups: all keys, and a window of 100 keys.  While a sequence grows, the windowed
+    group holds only the blocks from (length - window + 1) // PAGE on; no page is lost, held
+    twice or given back twice, and everything returns when the slot is freed."""
+    W = 100
+    kv = [KVRequest(2, 16), KVRequest(2, 16, window=W)]
+    c = SequenceCache(kv, [None] * 2, [None] * 2, max_tokens=PAGE * 32, max_seq_len=PAGE * 16, dtype=torch.float32, device="cpu")
+    full, win = c.groups
+    a, b = c.alloc_slot(), c.alloc_slot()
+    lengths = {a: 0, b: 0}
+    rng = random.Random(5)
+    steps = [(a, 300), (b, 70)] + [(rng.choice([a, b]), 1) for _ in range(400)]
+    for slot, n in steps:
+        before = lengths[slot]
+        if before + n > c.max_seq_len:
+            continue
+        c.reserve(slot, before + n)
+        lengths[slot] = c.lengths[slot] = before + n
+        for s, length in lengths.items():
+            first_needed = max(0, (length - n if s == slot else length) - W + 1) // PAGE if length else 0
+            # the windowed group keeps every block a query of the step just reserved can read ...
+            assert all(p >= 0 for p in win.slot_pages[s][first_needed:])
+            # ... and has given back everything below the window as it stood before that step
+            assert win.first_block[s] <= first_needed
+            assert len(full.pages_of(s)) == pages_for(length, PAGE)
+        held = [p for s in lengths for p in win.pages_of(s)]
+        assert len(held) == len(set(held)) == win.pages.held()
+    assert win.first_block[a] > 0 and win.pages.held() < full.pages.held()
+    # a sequence's windowed blocks never exceed the window plus two straddled pages
+    assert all(len(win.pages_of(s)) <= pages_for(W, PAGE) + 2 for s in lengths)
+    c.free_slot(a)
+    c.free_slot(b)
+    assert c.pages_held() == [0, 0]
+    s2 = c.alloc_slot()
+    c.reserve(s2, 10)
+    assert win.first_block[s2] == 0 and len(win.pages_of(s2)) == 1
+
+
+def test_a_windowed_group_can_have_a_smaller_pool():
+    W = 100
+    kv = [KVRequest(2, 16), KVRequest(2, 16, window=W)]
+    c = SequenceCache(kv, [None] * 2, [None] * 2, max_tokens=PAGE * 64, max_seq_len=PAGE * 32, dtype=torch.float32, device="cpu",
+                      max_slots=2, window_step_tokens=PAGE)
+    assert c.pool_sizes() == [64, 2 * (pages_for(W + PAGE, PAGE) + 1)]
+    s = c.alloc_slot()
+    n = 0
+    for step in [PAGE] * 20 + [1] * 100:
+        c.reserve(s, n + step)
+        n = c.lengths[s] = n + step
+    assert c.pages_held()[0] == pages_for(n, PAGE) and c.pages_held()[1] <= pages_for(W + PAGE, PAGE) + 1
+    with pytest.raises(CacheError):
+        c.reserve(s, n + PAGE + 1)                          # more than the promised step
+    c.free_slot(s)
+    assert c.pages_held() == [0, 0]

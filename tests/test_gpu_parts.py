@@ -370,3 +370,79 @@ def test_toy_feed_forward_with_routing_and_toy_position_encoding():
         got += [engine.step([SequenceInput(slot, [t], [0])]) for t in tokens[33:]]
         engine.free_slot(slot)
     assert_close(torch.cat(got), ref, "float32", "toy routed feed-forward and absolute positions")
+
+
+def _windowed_reference(w, c, tokens, windows):
+    """The plain implementation with a window in some layers: a query at position p reads the
+    keys max(0, p - window + 1) .. p (``windows[layer]`` None: all keys)."""
+    inv = plain_llama.rope_inverse_frequencies(c["head_dim"], c["rope_theta"], c["rope_scaling"])
+    x = plain_llama.embedding(w["model.embed_tokens.weight"], tokens)
+    eps, T = c["rms_norm_eps"], len(tokens)
+    H, KV, hd = c["num_attention_heads"], c["num_key_value_heads"], c["head_dim"]
+    for layer, window in enumerate(windows):
+        p = f"model.layers.{layer}."
+        n = plain_llama.rmsnorm(x, w[p + "input_layernorm.weight"], eps)
+        if window is None:
+            x = x + plain_llama.attention_mixer(n, w, p, c, inv)
+        else:
+            pos = torch.arange(T)
+            q = plain_llama.rope_rotate((n @ w[p + "self_attn.q_proj.weight"].T).view(T, H, hd), pos, inv)
+            k = plain_llama.rope_rotate((n @ w[p + "self_attn.k_proj.weight"].T).view(T, KV, hd), pos, inv)
+            v = (n @ w[p + "self_attn.v_proj.weight"].T).view(T, KV, hd)
+            o = torch.empty(T, H, hd)
+            for t in range(T):
+                lo = max(0, t - window + 1)
+                o[t] = plain_llama.attention_scores_softmax_values(q[lo:t + 1], k[lo:t + 1], v[lo:t + 1])[-1]
+            x = x + o.reshape(T, H * hd) @ w[p + "self_attn.o_proj.weight"].T
+        x = x + plain_llama.swiglu_feed_forward(plain_llama.rmsnorm(x, w[p + "post_attention_layernorm.weight"], eps), w, p)
+    return plain_llama.output_logits(x, w, c)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_layers_with_a_window_beside_layers_without(dtype):
+    """Layer 1 of two reads all keys, layer 0 a window of 70: two cache groups, and the windowed
+    one gives pages back while the sequences grow (its pool is too small to hold them whole).
+    Pages given back by one sequence are taken by the other at once, so a kernel that read
+    below the window would read the other sequence's keys.  Two rounds: slots and pages reused."""
+    from kuiperllama_b200.config import PartSpec, config_from_dict
+    from kuiperllama_b200.engine import DecoderModel, Engine, SequenceInput, model_manifest
+    from kuiperllama_b200.parts import Runtime
+    from kuiperllama_b200.weights.random_init import random_tensor
+    W = 70
+    cfg = config_from_dict(config_dict("tiny3"))
+    spec = cfg.to_model_spec()
+    layers = list(spec.layers)
+    layers[0] = dataclasses.replace(layers[0], mixer=PartSpec("attention", dict(layers[0].mixer.params, window=W)))
+    spec = dataclasses.replace(spec, layers=tuple(layers))
+    manifest = model_manifest(spec)
+    tensors = {n: random_tensor(n, d, seed=9, std=0.05) for n, d in manifest.items()}
+    dt = torch.float32 if dtype == "float32" else torch.bfloat16
+    model = DecoderModel(spec, tensors, Runtime(DEV, dt))
+    cache = model.new_cache(max_tokens=64 * 12, max_seq_len=64 * 6, max_slots=2, window_step_tokens=130)
+    by_window = {g.request.window: g for g in cache.groups}
+    assert set(by_window) == {None, W} and by_window[W].pages.n == 2 * 5 < by_window[None].pages.n
+    engine = Engine(model, cache)
+    w = {k: v.to(dt).float() for k, v in tensors.items()}
+    c = dict(config_dict("tiny3"))
+    reqs = [random_tokens(n, cfg.vocab_size, seed=60 + n) for n in (330, 170)]
+    prompt = (130, 100)
+    with torch.inference_mode():
+        for round_ in range(2):
+            slots = [engine.alloc_slot() for _ in reqs]
+            first = engine.step([SequenceInput(s, r[:n], list(range(n))) for s, r, n in zip(slots, reqs, prompt)])
+            got = {0: [first[:prompt[0]]], 1: [first[prompt[0]:]]}
+            done = list(prompt)
+            while any(done[i] < len(reqs[i]) for i in (0, 1)):
+                live = [i for i in (0, 1) if done[i] < len(reqs[i])]
+                lg = engine.step([SequenceInput(slots[i], [reqs[i][done[i]]], [0]) for i in live])
+                for j, i in enumerate(live):
+                    got[i].append(lg[j:j + 1].clone())
+                    done[i] += 1
+            assert by_window[W].first_block[slots[0]] == (330 - 1 - W + 1) // 64 > 0
+            assert len(by_window[W].pages_of(slots[0])) <= 3 and len(by_window[None].pages_of(slots[0])) == 6
+            for s in slots:
+                engine.free_slot(s)
+            assert cache.pages_held() == [0, 0]
+            for i in (0, 1):
+                ref = _windowed_reference(w, c, reqs[i], [W, None])
+                assert_close(torch.cat(got[i]), ref, dtype, f"window in layer 0, request {i}, round {round_}")
