@@ -43,6 +43,29 @@ __device__ __forceinline__ float fast_exp2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+// sm_100 forms that halve the softmax's instruction count: a maximum of three, and float32 pairs
+// (two lanes of one 64-bit register) for multiply-add and add.
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+    uint64_t d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "f"(lo), "f"(hi));
+    return d;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
 __device__ __forceinline__ void tmem_st32(uint32_t addr, const uint32_t (&r)[32]) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
                  "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
@@ -260,7 +283,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                         for (int q = 0; q < 2; ++q)
 #pragma unroll
                             for (int e = 0; e < 32; e += 2)
-                                mx4[(e >> 1) & 3] = fmaxf(mx4[(e >> 1) & 3], fmaxf(__uint_as_float(sc[q][e]), __uint_as_float(sc[q][e + 1])));
+                                mx4[(e >> 1) & 3] = max3(mx4[(e >> 1) & 3], __uint_as_float(sc[q][e]), __uint_as_float(sc[q][e + 1]));
                     }
                 }
             const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * args.scale_log2;   // the scale is positive: it commutes with max
@@ -271,7 +294,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 factor = m_new == -INFINITY ? 1.f : fast_exp2(m_ref - m_new);     // 0 when nothing was seen before
             }
             const float muse = m_new == -INFINITY ? 0.f : m_new;
-            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+            uint64_t sum4[4] = {0ull, 0ull, 0ull, 0ull};                  // four chains of float32 pairs
+            const uint64_t scale2 = pack2(args.scale_log2, args.scale_log2), shift2 = pack2(-muse, -muse);
 #pragma unroll
             for (int h = 0; h < 2; ++h)
                 if (h * 64 < keys) {
@@ -283,13 +307,14 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                         uint32_t packed[16];
 #pragma unroll
                         for (int e = 0; e < 32; e += 2) {
-                            float p0 = fast_exp2(fmaf(__uint_as_float(sc[q][e]), args.scale_log2, -muse));
-                            float p1 = fast_exp2(fmaf(__uint_as_float(sc[q][e + 1]), args.scale_log2, -muse));
+                            float x0, x1;
+                            unpack2(fma2(pack2(__uint_as_float(sc[q][e]), __uint_as_float(sc[q][e + 1])), scale2, shift2), x0, x1);
+                            float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
                             if (need_mask) {
                                 if (h * 64 + q * 32 + e > limit) p0 = 0.f;
                                 if (h * 64 + q * 32 + e + 1 > limit) p1 = 0.f;
                             }
-                            sum4[(e >> 1) & 3] += p0 + p1;
+                            sum4[(e >> 1) & 3] = add2(sum4[(e >> 1) & 3], pack2(p0, p1));
                             __nv_bfloat162 pr = __floats2bfloat162_rn(p0, p1);
                             packed[e >> 1] = *reinterpret_cast<uint32_t*>(&pr);
                         }
@@ -297,7 +322,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                         tmem_st16(s_addr + h * 32 + q * 16, packed);
                     }
                 }
-            l = l * factor + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+            float sum_lo, sum_hi;
+            unpack2(add2(add2(sum4[0], sum4[1]), add2(sum4[2], sum4[3])), sum_lo, sum_hi);
+            l = l * factor + (sum_lo + sum_hi);
             m_ref = m_new;
             if (j > 0) {
                 // the output so far is complete (the scores of this block were issued after it); rescale if a row asks
