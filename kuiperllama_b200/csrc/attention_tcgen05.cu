@@ -134,12 +134,14 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int b = blockIdx.y, g = blockIdx.z;
+    const int b = blockIdx.y, g = blockIdx.x;
     const int H = args.H, KV = args.KV, Gp = args.Gp, G = H / KV;
     const int BT = AT_ROWS / Gp;                          // tokens per tile
     const int T = args.seq_new[b];
-    // long tiles first (CTAs are handed out in ascending blockIdx.x)
-    const int t0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * 2 * BT;
+    // Long tiles first: CTAs are handed out with blockIdx.x fastest and blockIdx.z slowest, so the
+    // token tile is z (descending) and every kv head's and sequence's longest tiles start before
+    // anybody's short ones.
+    const int t0 = ((int)gridDim.z - 1 - (int)blockIdx.z) * 2 * BT;
     if (t0 >= T) return;
     const int n_tiles = t0 + BT < T ? 2 : 1;
     const int start = args.seq_starts[b], slot = args.seq_slots[b], row0 = args.cu_tokens[b];
@@ -415,7 +417,7 @@ KL_API int kl_attention_tcgen05(const void* q, int q_stride, void* out, const vo
     }
     AttnArgs args{(bf16*)out, block_table, blocks_per_seq, cu_tokens, seq_slots, seq_starts, seq_new, H, KV, Gp,
                   scale * 1.4426950408889634f, status};
-    const dim3 grid((max_new + 2 * BT - 1) / (2 * BT), n_seqs, KV);          // two tiles of BT tokens per CTA
+    const dim3 grid(KV, n_seqs, (max_new + 2 * BT - 1) / (2 * BT));          // two tiles of BT tokens per CTA
     if (grid.y > 65535 || grid.z > 65535) return KL_ERR_BAD_SIZE;
     constexpr size_t smem = 2 * AT_Q_BYTES + 4 * AT_K_BYTES + 11 * 8 + 16 + 1024;
     static bool configured = false;
