@@ -56,9 +56,12 @@ class DecoderModel:
         else:
             self.lm_head = Linear(tensors[spec.lm_head_name], runtime)
         self.error_flag = torch.zeros(1, dtype=torch.int32, device=dev)
-        # In decode steps of the bfloat16 path a block may let its products add into the residual
-        # stream themselves and finish the norms in their epilogues (see parts/block.py).
-        self.stream_fusion = dt == torch.bfloat16
+        # Option (bfloat16 decode steps of a few tokens): a block lets its products add into the residual
+        # stream themselves and finish the norms in their epilogues (see parts/block.py).  It rounds
+        # the normalised rows differently from the norm kernel (bf16(x * w) * r instead of
+        # bf16(x * r * w)), so results would change in the last bit with the number of rows of a step,
+        # padding rows included; it is therefore off unless asked for.
+        self.stream_fusion = False
 
     def _build_layer(self, layer: LayerSpec, tensors):
         rt = self.runtime

@@ -180,6 +180,34 @@ def test_padding_rows_change_nothing(engines, dtype):
     assert_close(outs[1], ref, dtype, "tiny2 with padding rows")
 
 
+@pytest.mark.parametrize("name", ["tiny2", "tiny3"])
+def test_the_option_that_folds_the_norms_into_the_products(model_folders, name):
+    """bfloat16 decode steps of up to four sequences with ``stream_fusion``: the output and down
+    projections add into the residual stream themselves, the products after them apply 1 / rms
+    in their epilogue, and the two norm kernels of a layer are not launched.  Same logits as the
+    plain implementation within the bfloat16 tolerance."""
+    from kuiperllama_b200.csrc import ops
+    from kuiperllama_b200.engine import Engine, SequenceInput, load_model
+    folder = model_folders(name, seed=3)
+    vocab = config_dict(name)["vocab_size"]
+    reqs = [random_tokens(n, vocab, seed=900 + n) for n in (70, 41)]
+    launches = {}
+    for fusion in (False, True):
+        with torch.inference_mode():
+            model = load_model(folder, dtype="bfloat16", device="cuda:0")
+            model.stream_fusion = fusion
+            engine = Engine(model, model.new_cache(max_tokens=64 * 8))
+            before = ops.launch_count
+            got, _ = _run_batch(engine, reqs, [30, 30])
+            launches[fusion] = ops.launch_count - before
+        for g, r in zip(got, reqs):
+            assert_close(g, plain_logits(folder, r), "bfloat16", f"{name}, stream fusion {fusion}")
+    # every decode step saves at least one norm kernel per layer (which ones depends on the sizes:
+    # a product whose operands the tensor-core kernel refuses asks for the dense rows)
+    layers = config_dict(name)["num_hidden_layers"]
+    assert launches[False] - launches[True] >= 40 * (layers - 1) > 0, launches
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_logits_do_not_depend_on_the_cut_in_float32_order(engines, dtype):
     """Whole, split and batched runs of one request agree with each other far inside the
