@@ -531,6 +531,65 @@ def test_attention_mma_finds_one_far_key_among_thousands(ops, few_rows, splits):
                 _close(out[j].view(H, hd), want, "bfloat16", f"far key at {far}, query {j}")
 
 
+@pytest.mark.parametrize("kernel", ["simt_f32", "simt_bf16", "decode_split", "mma_prefill", "mma_decode", "fused_decode"])
+@pytest.mark.parametrize("window,n", [(100, 300), (64, 129), (65, 200), (1, 70)])
+def test_the_windows_edge_is_exact(ops, kernel, window, n):
+    """One key is made to dominate the softmax: first the key just outside the last query's
+    window (position p - window), which must not be seen at all, then the window's first key
+    (p - window + 1), whose value the output must then be.  Random scores would hide an edge
+    that is off by one inside the tolerance."""
+    from types import SimpleNamespace
+    torch.manual_seed(31)
+    H, KV, hd = 4, 2, 64
+    dt = torch.float32 if kernel == "simt_f32" else torch.bfloat16
+    name = "float32" if kernel == "simt_f32" else "bfloat16"
+    scale = 1 / math.sqrt(hd)
+    p_last = n - 1
+    new = 20 if kernel == "mma_prefill" else 1                  # query tokens: the last `new` positions
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+    for edge in (p_last - window, p_last - window + 1):
+        if edge < 0:
+            continue
+        k = torch.randn(n, KV, hd) * 0.1
+        v = torch.randn(n, KV, hd)
+        k[edge] = 0
+        k[edge, :, 9] = 40.0
+        q = torch.randn(new, H, hd) * 0.1
+        q[:, :, 9] = 40.0                                       # score 1600 / 8 = 200 at the edge key
+        cache = Paged(2, 320, KV, hd, dt, seed=8)
+        out = torch.empty(new, H * hd, device=DEV, dtype=dt)
+        if kernel == "fused_decode":
+            # the kernel writes the last token's key and value itself: give them as the projection's k and v
+            _fill_cache(cache, 1, k[:-1], v[:-1])
+            inv = torch.zeros(hd // 2, device=DEV)               # no rotation: angles are all zero
+            qkv = torch.cat([q[0].reshape(-1), k[-1].reshape(-1), v[-1].reshape(-1)])[None].to(dt).to(DEV)
+            step = SimpleNamespace(n_seqs=1, n_tokens=1, is_decode=True, cu_tokens=i32([0, 1]), seq_slots=i32([1]),
+                                   seq_starts=i32([p_last]), seq_new=i32([1]))
+            ops.attention_decode_fused(qkv, inv, out, cache.k, cache.v, cache.table, step, H, KV, hd, scale, window, 3)
+        else:
+            _fill_cache(cache, 1, k, v)
+            qbuf = q.view(new, H * hd).to(dt).to(DEV)
+            if kernel in ("simt_f32", "simt_bf16"):
+                ops.attention_simt(qbuf, H * hd, out, cache.k, cache.v, cache.table, i32([p_last]), i32([1]), 1, H, KV, hd, scale, window)
+            elif kernel == "decode_split":
+                ops.attention_decode(qbuf, H * hd, out, cache.k, cache.v, cache.table, i32([p_last]), i32([1]), 1, H, KV, hd, scale, window, 3)
+            else:
+                few = kernel == "mma_decode"
+                ops.attention_mma(qbuf, H * hd, out, cache.k, cache.v, cache.table, i32([0, new]), i32([1]), i32([n - new]), i32([new]),
+                                  1, new, new, H, KV, hd, scale, window, 3 if few else 1, few)
+        ops.check_status(out.device)
+        kk, vv = k.to(dt).float(), v.to(dt).float()
+        for j in range(new):
+            pos = n - new + j
+            qv = q[j].to(dt).float()
+            ref = _ref_attention(qv, kk, vv, pos, scale, window)
+            inside = pos - window + 1 <= edge <= pos
+            if inside:                                          # the reference itself is the edge key's value then
+                assert float((ref - vv[edge].double().repeat_interleave(H // KV, dim=0)).abs().max()) < 1e-6
+            _close(out[j].view(H, hd), ref, name, f"{kernel}: dominant key at {edge}, query at {pos}, window {window}",
+                   scale=float(vv.abs().max()))
+
+
 @pytest.mark.parametrize("M,I,K", [(1, 64, 64), (8, 512, 192), (33, 14336 // 8, 4096 // 8), (64, 128, 72), (65, 512, 192),
                                    (300, 1792, 520), (2048, 256, 4096)])
 def test_gate_up_product_with_swiglu_epilogue(ops, M, I, K):
