@@ -1,5 +1,5 @@
 // Causal grouped-query attention of a prefill step on the fifth-generation tensor cores
-// (bfloat16, head size 128): both products of flash attention as tcgen05.mma with their
+// (bfloat16, head sizes 64 and 128): both products of flash attention as tcgen05.mma with their
 // results in tensor memory.
 //
 // Per head: s_t = (q . k_t) * scale for lo <= t <= pos, softmax with the maximum subtracted,
@@ -9,8 +9,8 @@
 // A CTA owns two tiles of 128 query rows of one sequence and one kv head; a row is (token, head
 // of the kv group).  Warp 0 loads with TMA: the queries once (3-D boxes over [token, head, dim]),
 // then key blocks of two cache pages (128 keys) into a two-stage ring, keys and values as 64-wide
-// swizzled slabs.  Warp 1 issues the MMAs: S = Q K^T (M 128, N keys, K 128) into the tile's score
-// columns of tensor memory, and O += P V (M 128, N 128, K keys) into the tile's output columns,
+// swizzled slabs.  Warp 1 issues the MMAs: S = Q K^T (M 128, N keys, K head size) into the tile's score
+// columns of tensor memory, and O += P V (M 128, N head size, K keys) into the tile's output columns,
 // where P is read from tensor memory (the A operand) and V is the MN-major B operand, straight
 // from its [key][dim] rows.  Warps 2..5 are the softmax of tile 0, warps 6..9 of tile 1: thread r
 // owns row r of its tile.  It reads its 128 scores from tensor memory, takes exp2 against a
@@ -27,11 +27,8 @@
 namespace kl {
 
 constexpr int AT_ROWS = 128;             // query rows per CTA = UMMA M
-constexpr int AT_HD = 128;               // head size
 constexpr int AT_THREADS = 320;          // warp 0 loads, warp 1 issues, warps 2..5 and 6..9: softmax of tiles 0 and 1
 constexpr uint32_t AT_SLAB = AT_ROWS * 128;            // bytes of a [128 rows][64 elements] swizzled slab
-constexpr uint32_t AT_Q_BYTES = 2 * AT_SLAB;           // one tile's queries, 32 KB
-constexpr uint32_t AT_K_BYTES = 2 * AT_SLAB;           // [128 keys][128 dims] as two slabs
 constexpr float AT_RESCALE = 8.0f;                     // a row is rescaled when its maximum grew by more (log2 units)
 
 __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y, int z) {
@@ -115,9 +112,15 @@ struct AttnArgs {
     int* status;
 };
 
+// HD: head size, 64 or 128 (one or two 64-wide slabs per row of queries, keys and values).
+template <int HD>
 __global__ void __launch_bounds__(AT_THREADS, 1)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                          const __grid_constant__ CUtensorMap map_v, AttnArgs args) {
+    constexpr int AT_HD = HD;
+    constexpr int SLABS = HD / 64;
+    constexpr uint32_t AT_Q_BYTES = SLABS * AT_SLAB;      // one tile's queries
+    constexpr uint32_t AT_K_BYTES = SLABS * AT_SLAB;      // [128 keys][HD dims] as 64-wide slabs
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* q_sm = smem;                                 // [2 tiles]
@@ -179,18 +182,18 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         if (elect_one()) {
             mbar_expect_tx(q_full, n_tiles * AT_Q_BYTES);
             for (int t = 0; t < n_tiles; ++t) {
-                tma_load_3d(q_sm + t * AT_Q_BYTES, &map_q, q_full, 0, g * G, row0 + t0 + t * BT);
-                tma_load_3d(q_sm + t * AT_Q_BYTES + AT_SLAB, &map_q, q_full, 64, g * G, row0 + t0 + t * BT);
+                for (int h = 0; h < SLABS; ++h)
+                    tma_load_3d(q_sm + t * AT_Q_BYTES + h * AT_SLAB, &map_q, q_full, h * 64, g * G, row0 + t0 + t * BT);
             }
             int issued = 0;
             for (int j = 0; j < all_blocks; ++j) {
                 const int s = j & 1;
                 if (j >= 2 && !mbar_wait(&kv_empty[s], ((j >> 1) - 1) & 1, abort_flag, args.status, 11)) break;
                 const int pages = min(2, all_pages - 2 * j);
-                mbar_expect_tx(&kv_full[s], pages * 2 * (PAGE * 128 * 2));
+                mbar_expect_tx(&kv_full[s], pages * 2 * SLABS * (PAGE * 128));
                 for (int pg = 0; pg < pages; ++pg) {
                     const int y = (table[2 * j + pg] * KV + g) * PAGE;
-                    for (int h = 0; h < 2; ++h) {
+                    for (int h = 0; h < SLABS; ++h) {
                         tma_load_2d(k_sm + s * AT_K_BYTES + h * AT_SLAB + pg * (PAGE * 128), &map_k, &kv_full[s], h * 64, y);
                         tma_load_2d(v_sm + s * AT_K_BYTES + h * AT_SLAB + pg * (PAGE * 128), &map_v, &kv_full[s], h * 64, y);
                     }
@@ -387,15 +390,31 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 
 using namespace kl;
 
+namespace kl {
+template <int HD>
+static int launch_attention_tcgen05(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const AttnArgs& args,
+                                    dim3 grid, cudaStream_t stream) {
+    constexpr size_t smem = (size_t)(2 + 4) * (HD / 64) * AT_SLAB + 11 * 8 + 16 + 1024;     // two query tiles, two stages of keys and of values
+    static bool configured = false;
+    if (!configured) {
+        KL_CUDA(cudaFuncSetAttribute(attention_tcgen05_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured = true;
+    }
+    launch_kernel(attention_tcgen05_kernel<HD>, grid, AT_THREADS, smem, stream, mq, mk, mv, args);
+    KL_LAUNCH_CHECK();
+    return KL_OK;
+}
+}  // namespace kl
+
 // Prefill attention of a ragged batch (see kl_attention_mma for the arguments' meaning).  Head
-// size 128, group sizes that divide 128, no window; q rows 16-byte aligned.  Others:
+// sizes 64 and 128, group sizes that divide 128, no window; q rows 16-byte aligned.  Others:
 // KL_ERR_BAD_SIZE / KL_ERR_BAD_ALIGN, and the caller takes the mma.sync kernel.
 KL_API int kl_attention_tcgen05(const void* q, int q_stride, void* out, const void* k_cache, const void* v_cache,
                                 long long n_cache_rows, const int* block_table, int blocks_per_seq, const int* cu_tokens,
                                 const int* seq_slots, const int* seq_starts, const int* seq_new, int n_seqs, int max_new,
                                 int n_rows, int H, int KV, int hd, float scale, int* status, cudaStream_t stream) {
     if (n_seqs <= 0 || max_new <= 0) return KL_OK;
-    if (hd != AT_HD || KV <= 0 || H % KV) return KL_ERR_BAD_SIZE;
+    if ((hd != 64 && hd != 128) || KV <= 0 || H % KV) return KL_ERR_BAD_SIZE;
     const int G = H / KV;
     int Gp = 1;
     while (Gp < G) Gp <<= 1;
@@ -419,13 +438,6 @@ KL_API int kl_attention_tcgen05(const void* q, int q_stride, void* out, const vo
                   scale * 1.4426950408889634f, status};
     const dim3 grid(KV, n_seqs, (max_new + 2 * BT - 1) / (2 * BT));          // two tiles of BT tokens per CTA
     if (grid.y > 65535 || grid.z > 65535) return KL_ERR_BAD_SIZE;
-    constexpr size_t smem = 2 * AT_Q_BYTES + 4 * AT_K_BYTES + 11 * 8 + 16 + 1024;
-    static bool configured = false;
-    if (!configured) {
-        KL_CUDA(cudaFuncSetAttribute(attention_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        configured = true;
-    }
-    launch_kernel(attention_tcgen05_kernel, grid, AT_THREADS, smem, stream, mq, mk, mv, args);
-    KL_LAUNCH_CHECK();
-    return KL_OK;
+    return hd == 128 ? launch_attention_tcgen05<128>(mq, mk, mv, args, grid, stream)
+                     : launch_attention_tcgen05<64>(mq, mk, mv, args, grid, stream);
 }

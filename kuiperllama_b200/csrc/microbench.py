@@ -96,7 +96,7 @@ def main(argv=None) -> int:
             q = torch.randn(T, (H + 2 * KV) * hd, device=DEV).bfloat16()
             o = torch.empty(T, H * hd, device=DEV, dtype=torch.bfloat16)
             cu, sl, st, nw = i32([0, T]), i32([0]), i32([0]), i32([T])
-            if args.mma or hd != 128:
+            if args.mma or hd not in (64, 128):
                 fn = lambda: ops.attention_mma(q, q.shape[1], o, k, v, table, cu, sl, st, nw, 1, T, T, H, KV, hd, scale, 0, 1, False)
             else:
                 fn = lambda: ops.attention_tcgen05(q, q.shape[1], o, k, v, table, cu, sl, st, nw, 1, T, T, H, KV, hd, scale)

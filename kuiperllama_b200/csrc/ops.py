@@ -545,13 +545,13 @@ def attention_tcgen05(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache
                       block_table: torch.Tensor, cu_tokens: torch.Tensor, seq_slots: torch.Tensor, seq_starts: torch.Tensor,
                       seq_new: torch.Tensor, n_seqs: int, max_new: int, n_rows: int, num_heads: int, num_kv_heads: int,
                       head_dim: int, scale: float) -> None:
-    """Prefill attention with both products on tcgen05 (bfloat16, head size 128, no window)."""
+    """Prefill attention with both products on tcgen05 (bfloat16, head size 64 or 128, no window)."""
     _cuda(q, out, k_cache, v_cache, block_table, cu_tokens, seq_slots, seq_starts, seq_new)
     for t, nm in ((block_table, "block_table"), (cu_tokens, "cu_tokens"), (seq_slots, "seq_slots"),
                   (seq_starts, "seq_starts"), (seq_new, "seq_new")):
         _i32(t, nm)
     _need(q.dtype == out.dtype == k_cache.dtype == v_cache.dtype == torch.bfloat16, "attention_tcgen05: bfloat16 only")
-    _need(head_dim == 128 and q_stride % 8 == 0 and q.data_ptr() % 16 == 0, "attention_tcgen05: head_dim 128, aligned rows")
+    _need(head_dim in (64, 128) and q_stride % 8 == 0 and q.data_ptr() % 16 == 0, "attention_tcgen05: head_dim 64 or 128, aligned rows")
     _need(out.is_contiguous() and out.shape[0] >= n_rows and out.shape[1] == num_heads * head_dim, "attention_tcgen05: out shape")
     _need(k_cache.is_contiguous() and v_cache.is_contiguous()
           and tuple(k_cache.shape[1:]) == (num_kv_heads, PAGE, head_dim), "attention_tcgen05: cache layout")
@@ -564,7 +564,7 @@ def attention_tcgen05(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache
         "attention_tcgen05")
 
 
-# Which kernel prefill steps of the bfloat16 path use for head size 128: "tcgen05" or "mma".
+# Which kernel prefill steps of the bfloat16 path use for head sizes 64 and 128: "tcgen05" or "mma".
 PREFILL_KERNEL = "tcgen05"
 
 _counters: Dict[tuple, torch.Tensor] = {}
@@ -638,7 +638,7 @@ def attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache: torch.
     sizes, the split-KV kernel; float32 and everything else takes the plain kernel."""
     bf = q.dtype == torch.bfloat16
     group = num_heads // num_kv_heads
-    if (bf and not step.is_decode and PREFILL_KERNEL == "tcgen05" and head_dim == 128 and not window and group <= 128
+    if (bf and not step.is_decode and PREFILL_KERNEL == "tcgen05" and head_dim in (64, 128) and not window and group <= 128
             and q_stride % 8 == 0 and q.data_ptr() % 16 == 0 and step.max_new >= 8):
         attention_tcgen05(q, q_stride, out, k_cache, v_cache, block_table, step.cu_tokens, step.seq_slots, step.seq_starts,
                           step.seq_new, step.n_seqs, step.max_new, step.n_tokens, num_heads, num_kv_heads, head_dim, scale)

@@ -653,9 +653,9 @@ def test_attention_decode_fused(ops, H, KV, hd, window, splits, pieces):
     assert int(ops._zero_counters(torch.device(DEV), 1).abs().sum()) == 0
 
 
+@pytest.mark.parametrize("hd", [128, 64])
 @pytest.mark.parametrize("H,KV", [(8, 2), (32, 8), (4, 4), (6, 2), (8, 1), (16, 1)])
-def test_attention_tcgen05_prefill(ops, H, KV):
-    hd = 128
+def test_attention_tcgen05_prefill(ops, H, KV, hd):
     seqs = [(0, 150), (0, 1), (60, 70), (3, 64), (0, 65), (100, 5), (0, 300)]
     cache, slots, ks, vs, qbuf, stride, cu, sl, st, nw, rows = _ragged_problem(H, KV, hd, seqs, seed=21)
     out = torch.full((rows + 2, H * hd), 3.0, device=DEV, dtype=torch.bfloat16)
@@ -674,10 +674,11 @@ def test_attention_tcgen05_prefill(ops, H, KV):
             r += 1
 
 
-def test_attention_tcgen05_finds_one_far_key_among_thousands(ops):
+@pytest.mark.parametrize("hd", [128, 64])
+def test_attention_tcgen05_finds_one_far_key_among_thousands(ops, hd):
     torch.manual_seed(22)
     dt = torch.bfloat16
-    H, KV, hd, n, new = 8, 2, 128, 3000, 40
+    H, KV, n, new = 8, 2, 3000, 40
     for far in (0, 63, 64, 127, 128, 1999, 2999):
         cache = Paged(2, 3072, KV, hd, dt, seed=7)
         k = torch.randn(n, KV, hd) * 0.1
