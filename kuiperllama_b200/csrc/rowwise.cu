@@ -61,11 +61,22 @@ template <> struct Delta4<bf16> {
 };
 
 template <typename T, int THREADS, int VPT>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, 1)
 add_rmsnorm_kernel(float* __restrict__ residual, const T* __restrict__ delta, const float* __restrict__ partials,
                    int n_partials, size_t partial_stride, const float* __restrict__ weight, T* __restrict__ out,
                    const int* __restrict__ rows, int hidden, float eps) {
     pdl_launch_dependents();
+    // The norm's weight is written by no kernel: where a row fits the registers it is fetched before
+    // this grid waits for the kernel before it.
+    float4 wreg[VPT];
+    const bool fits = (hidden & 3) == 0 && (hidden >> 2) <= THREADS * VPT;
+    if (fits) {
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            const int i4 = threadIdx.x + j * THREADS;
+            wreg[j] = i4 < (hidden >> 2) ? *reinterpret_cast<const float4*>(weight + 4 * i4) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
     pdl_wait();
     __shared__ float scratch[33];
     const int r = blockIdx.x;
@@ -82,9 +93,16 @@ add_rmsnorm_kernel(float* __restrict__ residual, const T* __restrict__ delta, co
         auto value = [&](int i4) {
             float4 a = *reinterpret_cast<const float4*>(x + 4 * i4);
             if (d) { const float4 b = Delta4<T>::load(d + 4 * i4); a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w; }
-            for (int z = 0; z < n_partials; ++z) {
-                const float4 b = *reinterpret_cast<const float4*>(p + (size_t)z * partial_stride + 4 * i4);
-                a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+            // eight pieces are requested at a time (one trip to memory instead of eight) and added in ascending order
+            for (int z0 = 0; z0 < n_partials; z0 += 8) {
+                float4 b[8];
+#pragma unroll
+                for (int zz = 0; zz < 8; ++zz)
+                    b[zz] = z0 + zz < n_partials ? *reinterpret_cast<const float4*>(p + (size_t)(z0 + zz) * partial_stride + 4 * i4)
+                                                 : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int zz = 0; zz < 8; ++zz)
+                    if (z0 + zz < n_partials) { a.x += b[zz].x; a.y += b[zz].y; a.z += b[zz].z; a.w += b[zz].w; }
             }
             return a;
         };
@@ -115,7 +133,7 @@ add_rmsnorm_kernel(float* __restrict__ residual, const T* __restrict__ delta, co
             for (int j = 0; j < VPT; ++j) {
                 const int i4 = threadIdx.x + j * THREADS;
                 if (i4 < n4) {
-                    const float4 w = *reinterpret_cast<const float4*>(weight + 4 * i4);
+                    const float4 w = wreg[j];
                     const float4 a = v[j];
                     Delta4<T>::store(o + 4 * i4, make_float4(w.x * (a.x * inv), w.y * (a.y * inv), w.z * (a.z * inv), w.w * (a.w * inv)));
                 }
@@ -188,11 +206,11 @@ KL_API int kl_add_rmsnorm(float* residual, const void* delta, const float* parti
     if (n_partials < 0 || (n_partials > 0 && partials == nullptr)) return KL_ERR_BAD_SIZE;
     // few rows: more threads per row, so that a step of a handful of tokens is not one slow CTA each
     const bool wide = n_rows <= 256 && hidden >= 2048;
-#define KL_NORM(T, THREADS)                                                                                          \
-    launch_kernel(add_rmsnorm_kernel<T, THREADS, 8>, n_rows, THREADS, 0, stream, residual, (const T*)delta, partials, n_partials, \
+#define KL_NORM(T, THREADS, VPT)                                                                                        \
+    launch_kernel(add_rmsnorm_kernel<T, THREADS, VPT>, n_rows, THREADS, 0, stream, residual, (const T*)delta, partials, n_partials, \
         (size_t)partial_stride, weight, (T*)out, rows, hidden, eps)
-    if (dtype == KL_F32) { if (wide) KL_NORM(float, 1024); else KL_NORM(float, 256); }
-    else if (dtype == KL_BF16) { if (wide) KL_NORM(bf16, 1024); else KL_NORM(bf16, 256); }
+    if (dtype == KL_F32) { if (wide) KL_NORM(float, 1024, 2); else KL_NORM(float, 256, 8); }
+    else if (dtype == KL_BF16) { if (wide) KL_NORM(bf16, 1024, 2); else KL_NORM(bf16, 256, 8); }
     else return KL_ERR_BAD_DTYPE;
 #undef KL_NORM
     KL_LAUNCH_CHECK();
