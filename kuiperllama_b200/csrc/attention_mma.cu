@@ -537,7 +537,20 @@ static int attention_mma_dispatch(const void* q, int q_stride, void* out, const 
     return launch_mma<HD, WM, WN, NS>((const bf16*)q, q_stride, (bf16*)out, (const bf16*)k_cache, (const bf16*)v_cache,     \
                                   block_table, blocks_per_seq, cu_tokens, seq_slots, seq_starts, seq_new, part_o,      \
                                   part_ml, n_seqs, max_new, n_rows, H, KV, scale, window, splits, fuse, stream)
-    // two stages everywhere: a third one for decode (two CTAs per SM instead of three) measured slower
+    // Decode: three CTAs of two stages fit an SM, or two CTAs of three stages.  A CTA's time is set by
+    // its chain of pages either way, so what counts is how many rounds of CTAs the grid needs: three
+    // stages where they do not add a round (64 sequences of 8 kv heads: 2 rounds both ways, 47 against 53 us).
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0;
+        KL_CUDA(cudaGetDevice(&dev));
+        KL_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    }
+    if (hd == 128 && few_rows) {
+        const long long ctas = (long long)n_seqs * KV * splits;
+        const long long rounds2 = (ctas + 3 * sms - 1) / (3 * sms), rounds3 = (ctas + 2 * sms - 1) / (2 * sms);
+        if (rounds2 > 1 && rounds3 <= rounds2) KL_MMA(128, 1, 4, 3);
+    }
     if (hd == 128) { if (few_rows) KL_MMA(128, 1, 4, 2); else KL_MMA(128, 4, 1, 2); }
     if (hd == 64) { if (few_rows) KL_MMA(64, 1, 4, 2); else KL_MMA(64, 4, 1, 2); }
 #undef KL_MMA
