@@ -52,10 +52,17 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 template <int HD, int THREADS>
 __device__ __forceinline__ void load_page(bf16* stage, const bf16* __restrict__ src) {
     constexpr int CHUNKS = HD / 8;                       // 16-byte chunks per row
-    for (int i = threadIdx.x; i < PAGE * CHUNKS; i += THREADS) {
-        const int r = i / CHUNKS, c = i % CHUNKS;
-        cp_async16(stage + r * HD + ((c ^ (r & 7)) << 3), src + r * HD + (c << 3));
-    }
+    constexpr int ROWS_PER_TURN = THREADS / CHUNKS;      // rows that the CTA covers with one copy per thread
+    static_assert(THREADS % CHUNKS == 0 && ROWS_PER_TURN % 8 == 0 && PAGE % ROWS_PER_TURN == 0, "load_page: thread layout");
+    // A thread keeps its chunk column; its rows are ROWS_PER_TURN apart, a multiple of 8, so the
+    // swizzle term is the same in every turn and the addresses differ by compile-time constants.
+    const int r0 = threadIdx.x / CHUNKS, c = threadIdx.x % CHUNKS;
+    const uint32_t dst = smem_addr(stage + r0 * HD + ((c ^ (r0 & 7)) << 3));
+    const bf16* from = src + r0 * HD + (c << 3);
+#pragma unroll
+    for (int t = 0; t < PAGE / ROWS_PER_TURN; ++t)
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;"
+                     ::"r"(dst + (uint32_t)(t * ROWS_PER_TURN * HD * 2)), "l"(from + t * ROWS_PER_TURN * HD) : "memory");
 }
 
 // What a decode step may fold into the attention kernel (one token per sequence): the sum of
@@ -318,7 +325,10 @@ attention_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict_
                 l[i] *= corr[i];
             }
 #pragma unroll
-            for (int n = 0; n < ON; ++n) { o[n][0] *= corr[0]; o[n][1] *= corr[0]; o[n][2] *= corr[1]; o[n][3] *= corr[1]; }
+            if (__any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f)) {      // most blocks after the first leave the maxima alone
+#pragma unroll
+                for (int n = 0; n < ON; ++n) { o[n][0] *= corr[0]; o[n][1] *= corr[0]; o[n][2] *= corr[1]; o[n][3] *= corr[1]; }
+            }
 #pragma unroll
             for (int n = 0; n < NT; ++n) {
 #pragma unroll
