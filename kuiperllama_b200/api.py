@@ -73,7 +73,7 @@ class LlamaInfer:
 
 def load(path: Optional[str] = None, dtype: str = "bfloat16", device: str = "cuda:0", *, config=None,
          random_weights: bool = False, seed: int = 0, max_tokens: Optional[int] = None, max_batch: int = 64,
-         max_seq_len: Optional[int] = None, use_graphs: bool = True) -> LlamaInfer:
+         max_seq_len: Optional[int] = None, use_graphs: bool = True, stream_fusion: bool = False) -> LlamaInfer:
     """Load the model folder ``path`` (config.json + model.safetensors).  With
     ``random_weights`` and a ``config`` object, build a random model on the device instead."""
     if random_weights:
@@ -85,4 +85,5 @@ def load(path: Optional[str] = None, dtype: str = "bfloat16", device: str = "cud
         if path is None:
             raise ValueError("load() needs a model folder, or random_weights=True with a config")
         model = load_model(path, dtype=dtype, device=device)
-    return LlamaInfer(model, max_tokens=max_tokens, max_batch=max_batch, max_seq_len=max_seq_len, use_graphs=use_graphs)
+    return LlamaInfer(model, max_tokens=max_tokens, max_batch=max_batch, max_seq_len=max_seq_len, use_graphs=use_graphs,
+                      stream_fusion=stream_fusion)

@@ -41,6 +41,8 @@ def main(argv: Optional[List[str]] = None) -> int:
     ap.add_argument("--max-batch", type=int, default=64)
     ap.add_argument("--max-ctx", type=int, default=None, help="longest sequence the cache holds")
     ap.add_argument("--device", default="cuda:0")
+    ap.add_argument("--stream-fusion", action="store_true",
+                    help="decode steps of up to 4 sequences fold the residual add and the norms into the products")
     args = ap.parse_args(argv)
 
     import torch
@@ -51,7 +53,7 @@ def main(argv: Optional[List[str]] = None) -> int:
         import sentencepiece
         tok = sentencepiece.SentencePieceProcessor(model_file=args.tokenizer)
     m = load(args.checkpoint, dtype=args.dtype, device=args.device, random_weights=args.random_weights, seed=args.seed,
-             max_batch=args.max_batch, max_seq_len=args.max_ctx)
+             max_batch=args.max_batch, max_seq_len=args.max_ctx, stream_fusion=args.stream_fusion)
     prompts: List[List[int]] = [_ids(p) for p in args.prompt_ids]
     if args.random_prompts:
         b, n = (int(x) for x in args.random_prompts.split(":"))
