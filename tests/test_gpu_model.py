@@ -22,7 +22,7 @@ def engines(model_folders):
     made = {}
 
     def get(name: str, dtype: str, max_tokens: int = 64 * 48):
-        key = (name, dtype)
+        key = (name, dtype, max_tokens)
         if key not in made:
             folder = model_folders(name, seed={"tiny1": 0, "tiny2": 1, "tiny3": 2}[name])
             with torch.inference_mode():
@@ -178,6 +178,18 @@ def test_padding_rows_change_nothing(engines, dtype):
     assert torch.equal(outs[0], outs[1]), "padding rows changed a logit"
     ref = torch.cat([plain_logits(folder, r)[:-1] for r in reqs] + [plain_logits(folder, r)[-1:] for r in reqs], dim=0)
     assert_close(outs[1], ref, dtype, "tiny2 with padding rows")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_batch_of_more_than_64_sequences(engines, dtype):
+    """70 sequences of unequal lengths: their prompts in one step (more than 64 rows, ragged),
+    then decode steps of 70 rows, which take the kernels for many tokens instead of those for few."""
+    engine, folder = engines("tiny1", dtype, max_tokens=64 * 80)
+    vocab = config_dict("tiny1")["vocab_size"]
+    reqs = [random_tokens(4 + (i * 7) % 9, vocab, seed=1200 + i) for i in range(70)]
+    got, _ = _run_batch(engine, reqs, [len(r) - 3 for r in reqs])
+    for i in (0, 1, 33, 64, 65, 69):
+        assert_close(got[i], plain_logits(folder, reqs[i]), dtype, f"tiny1 {dtype}: sequence {i} of 70")
 
 
 @pytest.mark.parametrize("name", ["tiny2", "tiny3"])
