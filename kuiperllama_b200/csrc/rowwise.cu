@@ -68,8 +68,10 @@ add_rmsnorm_kernel(float* __restrict__ residual, const T* __restrict__ delta, co
     pdl_launch_dependents();
     // The norm's weight is written by no kernel: where a row fits the registers it is fetched before
     // this grid waits for the kernel before it.
-    float4 wreg[VPT];
-    const bool fits = (hidden & 3) == 0 && (hidden >> 2) <= THREADS * VPT;
+    // (only in the form for few rows, THREADS = 1024: with many rows the registers are worth more as occupancy)
+    constexpr bool FEW = THREADS >= 1024;
+    float4 wreg[FEW ? VPT : 1];
+    const bool fits = FEW && (hidden & 3) == 0 && (hidden >> 2) <= THREADS * VPT;
     if (fits) {
 #pragma unroll
         for (int j = 0; j < VPT; ++j) {
@@ -93,15 +95,16 @@ add_rmsnorm_kernel(float* __restrict__ residual, const T* __restrict__ delta, co
         auto value = [&](int i4) {
             float4 a = *reinterpret_cast<const float4*>(x + 4 * i4);
             if (d) { const float4 b = Delta4<T>::load(d + 4 * i4); a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w; }
-            // eight pieces are requested at a time (one trip to memory instead of eight) and added in ascending order
-            for (int z0 = 0; z0 < n_partials; z0 += 8) {
-                float4 b[8];
+            // eight pieces (few rows) are requested at a time, one trip to memory instead of eight, and added in ascending order
+            constexpr int ZB = FEW ? 8 : 2;
+            for (int z0 = 0; z0 < n_partials; z0 += ZB) {
+                float4 b[ZB];
 #pragma unroll
-                for (int zz = 0; zz < 8; ++zz)
+                for (int zz = 0; zz < ZB; ++zz)
                     b[zz] = z0 + zz < n_partials ? *reinterpret_cast<const float4*>(p + (size_t)(z0 + zz) * partial_stride + 4 * i4)
                                                  : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-                for (int zz = 0; zz < 8; ++zz)
+                for (int zz = 0; zz < ZB; ++zz)
                     if (z0 + zz < n_partials) { a.x += b[zz].x; a.y += b[zz].y; a.z += b[zz].z; a.w += b[zz].w; }
             }
             return a;
@@ -133,7 +136,7 @@ add_rmsnorm_kernel(float* __restrict__ residual, const T* __restrict__ delta, co
             for (int j = 0; j < VPT; ++j) {
                 const int i4 = threadIdx.x + j * THREADS;
                 if (i4 < n4) {
-                    const float4 w = wreg[j];
+                    const float4 w = FEW ? wreg[FEW ? j : 0] : *reinterpret_cast<const float4*>(weight + 4 * i4);
                     const float4 a = v[j];
                     Delta4<T>::store(o + 4 * i4, make_float4(w.x * (a.x * inv), w.y * (a.y * inv), w.z * (a.z * inv), w.w * (a.w * inv)));
                 }
