@@ -212,8 +212,10 @@ KL_API int kl_add_rmsnorm(float* residual, const void* delta, const float* parti
 #define KL_NORM(T, THREADS, VPT)                                                                                        \
     launch_kernel(add_rmsnorm_kernel<T, THREADS, VPT>, n_rows, THREADS, 0, stream, residual, (const T*)delta, partials, n_partials, \
         (size_t)partial_stride, weight, (T*)out, rows, hidden, eps)
-    if (dtype == KL_F32) { if (wide) KL_NORM(float, 1024, 2); else KL_NORM(float, 256, 8); }
-    else if (dtype == KL_BF16) { if (wide) KL_NORM(bf16, 1024, 2); else KL_NORM(bf16, 256, 8); }
+    // many rows: a row in registers of 256 threads, four or eight float4 each (fewer registers, more CTAs per SM)
+    const bool narrow = hidden <= 256 * 4 * 4;
+    if (dtype == KL_F32) { if (wide) KL_NORM(float, 1024, 2); else if (narrow) KL_NORM(float, 256, 4); else KL_NORM(float, 256, 8); }
+    else if (dtype == KL_BF16) { if (wide) KL_NORM(bf16, 1024, 2); else if (narrow) KL_NORM(bf16, 256, 4); else KL_NORM(bf16, 256, 8); }
     else return KL_ERR_BAD_DTYPE;
 #undef KL_NORM
     KL_LAUNCH_CHECK();
