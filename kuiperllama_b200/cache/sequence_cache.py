@@ -32,7 +32,8 @@ PAGE = 64      # tokens per page; the kernels are compiled for the same number
 
 @dataclass(frozen=True)
 class KVRequest:
-    """Token-indexed storage a mixer asks for.  ``kind`` "full": keys are stored by position.
+    """Token-indexed storage a mixer asks for.  ``kind`` names a registered storage class
+    (``register_cache_kind``); "full": keys are stored by position in pages.
     ``window`` is the number of most recent keys the mixer reads (None: all); with a window
     the pages that no query can reach any more are given back while the sequence grows."""
     kv_heads: int
@@ -58,13 +59,48 @@ class CacheView:
     writable: bool                        # False: the execution reads another one's cache
 
 
-class _Group:
+_KINDS: Dict[str, type] = {}
+
+
+def register_cache_kind(name: str):
+    """Class decorator: token-indexed storage of the kind ``KVRequest.kind`` names.  The class is
+    built as ``cls(request, entries, max_tokens_pages, n_slots, blocks_per_seq, dtype, device,
+    window_step_tokens)`` for the schedule entries whose requests are equal, and offers
+
+    * ``reserve(slot, old_length, new_length)``: room for the sequence to grow (raises CacheError),
+    * ``release(slot)``: everything the sequence holds goes back,
+    * ``flush()``: bring device-side tables up to date on the current stream,
+    * ``view(j) -> (k, v, block_table)``: what execution ``entries[j]`` sees,
+    * ``held() -> int`` and ``pool_size() -> int`` for the accounting, ``bytes() -> int``.
+    """
+    def deco(cls: type) -> type:
+        _KINDS[name] = cls
+        return cls
+    return deco
+
+
+def cache_kind(name: str) -> type:
+    try:
+        return _KINDS[name]
+    except KeyError:
+        raise CacheError(f"cache kind {name!r} is not known (known: {', '.join(sorted(_KINDS))})") from None
+
+
+@register_cache_kind("full")
+class PagedGroup:
+    """Keys and values stored by position in pages of ``PAGE`` tokens,
+    ``[executions, pages, kv_heads, PAGE, head_dim]``, with a block table per slot.  With a
+    ``window`` in the request, pages that no query can reach any more go back to the pool while
+    the sequence grows."""
+
     def __init__(self, request: KVRequest, entries: List[int], n_pages: int, n_slots: int, blocks_per_seq: int,
-                 dtype: torch.dtype, device: torch.device):
-        if request.kind != "full":
-            raise CacheError(f"cache kind {request.kind!r} is not known (known: 'full')")
+                 dtype: torch.dtype, device: torch.device, window_step_tokens: Optional[int] = None):
         self.request = request
         self.entries = entries
+        if request.window is not None and window_step_tokens is not None:
+            # the window's keys and the step's new tokens, both possibly straddling page borders
+            per_slot = pages_for(request.window + window_step_tokens, PAGE) + 1
+            n_pages = max(1, min(n_pages, n_slots * per_slot))
         self.pages = FreeList(n_pages, "page")
         self.blocks_per_seq = blocks_per_seq
         shape = (len(entries), n_pages, request.kv_heads, PAGE, request.head_dim)
@@ -83,6 +119,49 @@ class _Group:
     def pages_of(self, slot: int) -> List[int]:
         """The pages the sequence in ``slot`` holds now."""
         return [p for p in self.slot_pages[slot] if p >= 0]
+
+    def reserve(self, slot: int, old_length: int, new_length: int) -> None:
+        have = self.slot_pages[slot]
+        if self.request.window is not None:
+            # the first key any query of this step (positions old_length and up) or of a later
+            # one reads is old_length - window + 1: whole blocks below it go back to the pool
+            keep_from = min(max(0, old_length - self.request.window + 1) // PAGE, len(have))
+            for b in range(self.first_block[slot], keep_from):
+                self.pages.give_back(have[b])
+                have[b] = -1
+            self.first_block[slot] = max(self.first_block[slot], keep_from)
+        need = pages_for(new_length, PAGE)
+        if need > len(have):
+            fresh = self.pages.take_many(need - len(have))
+            for p in fresh:
+                self.table_host[slot, len(have)] = p
+                have.append(p)
+            self.dirty.add(slot)
+
+    def release(self, slot: int) -> None:
+        for p in reversed(self.pages_of(slot)):
+            self.pages.give_back(p)
+        self.slot_pages[slot] = []
+        self.first_block[slot] = 0
+
+    def flush(self) -> None:
+        if not self.dirty:
+            return
+        lo, hi = min(self.dirty), max(self.dirty) + 1
+        self.table[lo:hi].copy_(self.table_host[lo:hi], non_blocking=True)
+        self.dirty.clear()
+
+    def view(self, j: int):
+        return self.k[j], self.v[j], self.table
+
+    def held(self) -> int:
+        return self.pages.held()
+
+    def pool_size(self) -> int:
+        return self.pages.n
+
+    def bytes(self) -> int:
+        return self.k.numel() * self.k.element_size() * 2
 
 
 class SequenceCache:
@@ -116,18 +195,12 @@ class SequenceCache:
         for i, (req, src) in enumerate(zip(kv_requests, cache_from)):
             if req is not None and src is None:
                 by_request.setdefault(req, []).append(i)
-        def pool_size(req: KVRequest) -> int:
-            if req.window is None or window_step_tokens is None:
-                return self.n_pages
-            # the window's keys and the step's new tokens, both possibly straddling page borders
-            per_slot = pages_for(req.window + window_step_tokens, PAGE) + 1
-            return max(1, min(self.n_pages, self.n_slots * per_slot))
-
         self.window_step_tokens = window_step_tokens
-        self.groups: List[_Group] = [
-            _Group(req, entries, pool_size(req), self.n_slots, self.blocks_per_seq, dtype, self.device)
+        self.groups = [
+            cache_kind(req.kind)(req, entries, self.n_pages, self.n_slots, self.blocks_per_seq, dtype, self.device,
+                                 window_step_tokens)
             for req, entries in by_request.items()]
-        self._where: Dict[int, Tuple[_Group, int]] = {}
+        self._where: Dict[int, Tuple[object, int]] = {}
         for g in self.groups:
             for j, e in enumerate(g.entries):
                 self._where[e] = (g, j)
@@ -155,10 +228,7 @@ class SequenceCache:
         if not self.slots.is_held(slot):
             raise CacheError(f"slot {slot} is freed but is not held")
         for g in self.groups:
-            for p in reversed(g.pages_of(slot)):
-                g.pages.give_back(p)
-            g.slot_pages[slot] = []
-            g.first_block[slot] = 0
+            g.release(slot)
         self.lengths[slot] = 0
         self.slots.give_back(slot)
 
@@ -171,32 +241,13 @@ class SequenceCache:
             raise CacheError(f"a sequence of {new_length} tokens exceeds the cache's limit of {self.max_seq_len}")
         if self.window_step_tokens is not None and new_length - self.lengths[slot] > self.window_step_tokens:
             raise CacheError(f"a step of {new_length - self.lengths[slot]} tokens exceeds the promised {self.window_step_tokens}")
-        need = pages_for(new_length, PAGE)
         for g in self.groups:
-            have = g.slot_pages[slot]
-            if g.request.window is not None:
-                # the first key any query of this step (positions lengths[slot] and up) or of a later
-                # one reads is lengths[slot] - window + 1: whole blocks below it go back to the pool
-                keep_from = min(max(0, self.lengths[slot] - g.request.window + 1) // PAGE, len(have))
-                for b in range(g.first_block[slot], keep_from):
-                    g.pages.give_back(have[b])
-                    have[b] = -1
-                g.first_block[slot] = max(g.first_block[slot], keep_from)
-            if need > len(have):
-                fresh = g.pages.take_many(need - len(have))
-                for p in fresh:
-                    g.table_host[slot, len(have)] = p
-                    have.append(p)
-                g.dirty.add(slot)
+            g.reserve(slot, self.lengths[slot], new_length)
 
     def flush_tables(self) -> None:
         """Bring the device's block tables up to date (copies on the current stream)."""
         for g in self.groups:
-            if not g.dirty:
-                continue
-            lo, hi = min(g.dirty), max(g.dirty) + 1
-            g.table[lo:hi].copy_(g.table_host[lo:hi], non_blocking=True)
-            g.dirty.clear()
+            g.flush()
 
     # ------------------------------------------------------------------ views
     def view(self, entry: int) -> CacheView:
@@ -205,7 +256,7 @@ class SequenceCache:
         k = v = table = None
         if owner in self._where:
             g, j = self._where[owner]
-            k, v, table = g.k[j], g.v[j], g.table
+            k, v, table = g.view(j)
         return CacheView(k=k, v=v, block_table=table, state=self.states.get(owner), writable=src is None)
 
     # ------------------------------------------------------------------ accounting
@@ -214,11 +265,11 @@ class SequenceCache:
         return sum(pages_for(self.lengths[s], PAGE) * PAGE for s in range(self.n_slots) if self.slots.is_held(s))
 
     def pages_held(self) -> List[int]:
-        return [g.pages.held() for g in self.groups]
+        return [g.held() for g in self.groups]
 
     def pool_sizes(self) -> List[int]:
-        return [g.pages.n for g in self.groups]
+        return [g.pool_size() for g in self.groups]
 
     def bytes(self) -> int:
-        n = sum(g.k.numel() * g.k.element_size() * 2 for g in self.groups)
+        n = sum(g.bytes() for g in self.groups)
         return n + sum(s.numel() * s.element_size() for s in self.states.values())

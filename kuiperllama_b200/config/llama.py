@@ -228,6 +228,8 @@ class LlamaConfig:
             embedding_name="model.embed_tokens.weight",
             final_norm=PartSpec("rmsnorm", {**norm.params, "name": "weight"}), final_norm_prefix="model.norm.",
             lm_head_name=None if self.tie_word_embeddings else "lm_head.weight",
-            stop_token_ids=self.eos_token_ids, bos_token_id=self.bos_token_id)
+            stop_token_ids=self.eos_token_ids, bos_token_id=self.bos_token_id,
+            # exporters of Llama checkpoints may write rotary tables, and a classifier beside a tied table
+            ignorable_suffixes=("rotary_emb.inv_freq",) + (("lm_head.weight",) if self.tie_word_embeddings else ()))
         spec.validate()
         return spec

@@ -51,6 +51,13 @@ def config_from_folder(folder: str):
     path = os.path.join(folder, "config.json")
     if not os.path.isfile(path):
         raise ConfigError(f"no config.json in {folder!r}")
+    return config_from_file(path)
+
+
+def config_from_file(path: str):
+    """The typed configuration of a config.json given by its own path."""
+    if not os.path.isfile(path):
+        raise ConfigError(f"no such configuration file: {path!r}")
     with open(path) as f:
         try:
             d = json.load(f)

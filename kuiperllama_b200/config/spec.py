@@ -62,10 +62,18 @@ class ModelSpec:
     lm_head_name: Optional[str]      # None: tied to the embedding table
     stop_token_ids: Tuple[int, ...] = ()
     bos_token_id: Optional[int] = None
+    # Tensor-name endings a checkpoint of this architecture may hold without the model reading them.
+    ignorable_suffixes: Tuple[str, ...] = ()
+    # Options that some decoders have around the layers; None leaves the step out.
+    embedding_multiplier: Optional[float] = None     # x = multiplier * E[token]
+    logit_scale: Optional[float] = None              # logits = scale * (W_cls x)
+    logit_softcap: Optional[float] = None            # logits = cap * tanh(logits / cap), after the scale
 
     def validate(self) -> None:
         if not self.layers:
             raise ValueError("a model needs at least one layer")
+        if self.logit_softcap is not None and not self.logit_softcap > 0:
+            raise ValueError(f"logit_softcap must be positive, got {self.logit_softcap}")
         for i, e in enumerate(self.schedule):
             if not 0 <= e.layer < len(self.layers):
                 raise ValueError(f"schedule[{i}] names layer {e.layer}, but there are {len(self.layers)} layers")

@@ -550,12 +550,8 @@ static int attention_mma_dispatch(const void* q, int q_stride, void* out, const 
     // Decode: three CTAs of two stages fit an SM, or two CTAs of three stages.  A CTA's time is set by
     // its chain of pages either way, so what counts is how many rounds of CTAs the grid needs: three
     // stages where they do not add a round (64 sequences of 8 kv heads: 2 rounds both ways, 47 against 53 us).
-    static int sms = 0;
-    if (sms == 0) {
-        int dev = 0;
-        KL_CUDA(cudaGetDevice(&dev));
-        KL_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-    }
+    const int sms = kl::sm_count();
+    if (sms <= 0) return KL_ERR_SETUP;
     if (hd == 128 && few_rows) {
         const long long ctas = (long long)n_seqs * KV * splits;
         const long long rounds2 = (ctas + 3 * sms - 1) / (3 * sms), rounds3 = (ctas + 2 * sms - 1) / (2 * sms);

@@ -77,6 +77,27 @@ inline void launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_
     cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
+// Streaming multiprocessors of the current device (asked of the driver once per device; 0 on error).
+inline int sm_count() {
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+// Grid of a grid-stride kernel over `items`: enough CTAs of `threads` for all of them, at most
+// `per_sm` for every multiprocessor of the device.
+inline int strided_grid(size_t items, int threads, int per_sm) {
+    const size_t need = (items + threads - 1) / threads;
+    const size_t cap = (size_t)(sm_count() > 0 ? sm_count() : 1) * per_sm;
+    return (int)(need < cap ? need : cap);
+}
+
 __device__ __forceinline__ float to_f32(float v) { return v; }
 __device__ __forceinline__ float to_f32(bf16 v) { return __bfloat162float(v); }
 

@@ -164,6 +164,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         // ---------------------------------------------------------------- MMA issuer
         if (elect_one()) {
             constexpr uint32_t idesc = umma_idesc(BN);
+            // No stage can fill before the kernel ahead has finished (the activations are requested
+            // after the loader's own wait), so wait for it here too: the bounded polls below then
+            // count this kernel's own progress only.
+            pdl_wait();
             bool ok = true;
             int it = 0, lt = 0;                               // k blocks consumed, tiles done (both over all tiles)
             for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++lt) {
@@ -484,12 +488,8 @@ KL_API int kl_gemm_tcgen05(const void* a, long long lda, const void* w, long lon
     const int tiles_m = (M + TC_BM - 1) / TC_BM, tiles_n = (N + 255) / 256;
     GemmArgs args{out, ldo, 0, M, N, (K + TC_BK - 1) / TC_BK, out_f32, status, tiles_m, tiles_n, swiglu};
     if ((long long)tiles_m * tiles_n > 0x7fffffffLL) return KL_ERR_BAD_SIZE;
-    static int sms = 0;
-    if (sms == 0) {
-        int dev = 0;
-        KL_CUDA(cudaGetDevice(&dev));
-        KL_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-    }
+    const int sms = kl::sm_count();
+    if (sms <= 0) return KL_ERR_SETUP;
     dim3 grid(min(tiles_m * tiles_n, sms), 1, 1);      // one CTA per SM walks the tiles
     return launch<256, 4, false>(ma, mb, args, grid, stream);
 }
@@ -556,7 +556,7 @@ KL_API int kl_splitk_reduce(const float* partial, int splits, int M, int N, void
     if (M <= 0 || N <= 0) return KL_OK;
     const size_t total = (size_t)M * N;
     const int threads = 256;
-    const int blocks = (int)((total + threads - 1) / threads < 148 * 8 ? (total + threads - 1) / threads : 148 * 8);
+    const int blocks = kl::strided_grid(total, threads, 8);
     if (out_f32) launch_kernel(kl::splitk_reduce_kernel<float>, blocks, threads, 0, stream, partial, splits, M, N, (float*)out, ldo);
     else launch_kernel(kl::splitk_reduce_kernel<kl::bf16>, blocks, threads, 0, stream, partial, splits, M, N, (kl::bf16*)out, ldo);
     KL_LAUNCH_CHECK();

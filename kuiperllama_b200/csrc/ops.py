@@ -96,15 +96,27 @@ def _i32(t: Optional[torch.Tensor], name: str) -> None:
 
 # --------------------------------------------------------------------------- row-wise
 
-def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, error_flag: torch.Tensor) -> None:
-    """out[t] = float32(table[ids[t]]); ids outside the table set error_flag[0] = 1."""
+def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, error_flag: torch.Tensor,
+              scale: float = 1.0) -> None:
+    """out[t] = scale * float32(table[ids[t]]); ids outside the table set error_flag[0] = 1."""
     _cuda(ids, table, out, error_flag)
     _i32(ids, "ids"); _i32(error_flag, "error_flag")
     n, (vocab, hidden) = ids.numel(), table.shape
     _need(table.is_contiguous() and out.is_contiguous() and out.dtype == torch.float32, "embedding: bad layout")
     _need(out.shape[0] >= n and out.shape[1] == hidden, "embedding: output shape")
     _check(lib("rowwise").kl_embedding(_ptr(ids), n, _ptr(table), dtype_code(table.dtype), vocab, hidden,
-                                       _ptr(out), _ptr(error_flag), _stream()), "embedding")
+                                       ctypes.c_float(scale), _ptr(out), _ptr(error_flag), _stream()), "embedding")
+
+
+def logit_transform(logits: torch.Tensor, scale: float = 1.0, softcap: float = 0.0) -> None:
+    """In place on float32 logits [rows, vocab]: x = scale * x, then with ``softcap`` c > 0
+    x = c * tanh(x / c)."""
+    _cuda(logits)
+    _need(logits.dtype == torch.float32 and logits.dim() == 2 and logits.stride(1) == 1, "logit_transform: float32 rows")
+    _need(softcap >= 0.0, "logit_transform: the soft cap must not be negative")
+    rows, vocab = logits.shape
+    _check(lib("rowwise").kl_logit_transform(_ptr(logits), ctypes.c_longlong(logits.stride(0)), rows, vocab,
+                                             ctypes.c_float(scale), ctypes.c_float(softcap), _stream()), "logit_transform")
 
 
 def _partials(delta: Optional[torch.Tensor]) -> bool:
@@ -255,21 +267,65 @@ def sample_rows(logits: torch.Tensor, temperature: float, top_k: int, seed: int,
                                           _ptr(out), _stream()), "sample_rows")
 
 
+def token_logprob(logits: torch.Tensor, tokens: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """float32 [rows]: log softmax(logits[row])[tokens[row]]."""
+    _cuda(logits, tokens, out)
+    _i32(tokens, "tokens")
+    rows, vocab = logits.shape
+    _need(logits.dtype == torch.float32 and logits.stride(1) == 1 and tokens.numel() >= rows, "token_logprob: layout")
+    if out is None:
+        out = torch.empty(rows, dtype=torch.float32, device=logits.device)
+    _need(out.dtype == torch.float32 and out.is_contiguous() and out.numel() >= rows, "token_logprob: out")
+    _check(lib("sampling").kl_token_logprob(_ptr(logits), ctypes.c_longlong(logits.stride(0)), rows, vocab, _ptr(tokens),
+                                            _ptr(out), _stream()), "token_logprob")
+    return out
+
+
 # --------------------------------------------------------------------------- dispatch by dtype and shape
 
-_status_words: Dict[int, torch.Tensor] = {}
+_device_words: Dict[int, torch.Tensor] = {}
+
+
+def device_words(device: torch.device) -> torch.Tensor:
+    """Two int32 words per device through which kernels report what the host must not miss:
+    word 0 is the status word (kernels with bounded waits write a non-zero code into it when a
+    wait runs out), word 1 the flag that the embedding kernel sets when it meets a token id
+    outside the vocabulary.  ``check_device_words`` reads both with one copy."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx not in _device_words:
+        _device_words[idx] = torch.zeros(2, dtype=torch.int32, device=device)
+    return _device_words[idx]
 
 
 def status_word(device: torch.device) -> torch.Tensor:
-    """The device's int32 status word: kernels with bounded waits write a non-zero code into it
-    when a wait runs out.  ``check_status`` reads it (that synchronises)."""
-    idx = device.index if device.index is not None else torch.cuda.current_device()
-    if idx not in _status_words:
-        _status_words[idx] = torch.zeros(1, dtype=torch.int32, device=device)
-    return _status_words[idx]
+    return device_words(device)[0:1]
+
+
+def error_word(device: torch.device) -> torch.Tensor:
+    return device_words(device)[1:2]
+
+
+class TokenIdError(ValueError):
+    """A token id outside the vocabulary reached the embedding kernel."""
+
+
+def check_device_words(device: torch.device) -> None:
+    """Read both words (that synchronises), clear what was set, and raise for it: ``KernelError``
+    for a wait that ran out (whatever the kernels wrote after it is not to be trusted),
+    ``TokenIdError`` for a bad token id."""
+    words = device_words(device)
+    status, bad_id = words.tolist()
+    if status or bad_id:
+        words.zero_()
+    if status:
+        raise KernelError(f"a tensor-core kernel gave up waiting (code {status}: 1 = loader, 2 = MMA issuer, 3 = epilogue); "
+                          "the results of this run are not valid")
+    if bad_id:
+        raise TokenIdError("a token id outside the vocabulary reached the embedding kernel")
 
 
 def check_status(device: torch.device) -> None:
+    """The status word alone (the token-id flag is left as it is)."""
     word = status_word(device)
     code = int(word.item())
     if code:
@@ -287,7 +343,15 @@ def _tc_ok(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
             and out.stride(1) == 1)
 
 
-SM_COUNT = 148
+_sm_counts: Dict[int, int] = {}
+
+
+def sm_count(device: Optional[torch.device] = None) -> int:
+    """Streaming multiprocessors of ``device`` (default: the current one), asked of the driver once."""
+    idx = torch.cuda.current_device() if device is None or device.index is None else device.index
+    if idx not in _sm_counts:
+        _sm_counts[idx] = int(torch.cuda.get_device_properties(idx).multi_processor_count)
+    return _sm_counts[idx]
 
 
 def skinny_splits(N: int, K: int) -> int:
@@ -295,7 +359,7 @@ def skinny_splits(N: int, K: int) -> int:
     CTAs per SM stream weights: 128 output features per CTA, at least 4 k-blocks of 64 each."""
     tiles = (N + 127) // 128
     k_blocks = (K + 63) // 64
-    want = max(1, min((2 * SM_COUNT + tiles // 2) // tiles, k_blocks // 4, 32))
+    want = max(1, min((2 * sm_count() + tiles // 2) // tiles, k_blocks // 4, 32))
     per = (k_blocks + want - 1) // want
     return (k_blocks + per - 1) // per
 
@@ -462,7 +526,7 @@ def decode_splits(rows: int, num_heads: int, num_kv_heads: int) -> int:
     group = num_heads // num_kv_heads
     tiles = (group + 3) // 4 if group >= 3 else 1
     ctas = max(1, rows * num_kv_heads * tiles)
-    return max(1, min(32, (2 * SM_COUNT + ctas - 1) // ctas))
+    return max(1, min(32, (2 * sm_count() + ctas - 1) // ctas))
 
 
 def attention_decode(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
@@ -570,14 +634,19 @@ PREFILL_KERNEL = "tcgen05"
 _counters: Dict[tuple, torch.Tensor] = {}
 
 
+COUNTERS = 1 << 18     # int32 counters per device and use (1 MiB): one per (sequence, kv head) or per tile
+
+
 def _zero_counters(device: torch.device, n: int, use: str = "attention") -> torch.Tensor:
     """int32 counters that kernels leave at zero (the last CTA of a group resets its own); one
-    buffer per device and per use, so that kernels of different kinds never share a counter."""
+    buffer per device and per use, so that kernels of different kinds never share a counter.
+    The buffer is made once and never replaced: captured graphs and kernels in flight hold its
+    address."""
     idx = (device.index if device.index is not None else torch.cuda.current_device(), use)
     have = _counters.get(idx)
-    if have is None or have.numel() < n:
-        have = torch.zeros(max(n, 1 << 16), dtype=torch.int32, device=device)
-        _counters[idx] = have
+    if have is None:
+        have = _counters[idx] = torch.zeros(COUNTERS, dtype=torch.int32, device=device)
+    _need(n <= COUNTERS, f"{use}: {n} counters wanted, {COUNTERS} exist")
     return have
 
 
@@ -587,7 +656,7 @@ def decode_attention_splits(n_seqs: int, num_kv_heads: int) -> int:
     pages, so a second round costs more than longer chains (32 sequences of 8 kv heads: 27 us
     with one piece, 35 us with two)."""
     ctas = max(1, n_seqs * num_kv_heads)
-    return max(1, min(16, (3 * SM_COUNT) // ctas))
+    return max(1, min(16, (3 * sm_count()) // ctas))
 
 
 def decode_fusable(dtype: torch.dtype, head_dim: int, rotary_dim: int, num_heads: int, num_kv_heads: int) -> bool:

@@ -11,11 +11,12 @@
 
 namespace kl {
 
-// out[t, :] = table[ids[t], :] as float32.  An id outside [0, vocab) writes zeros and sets
-// *error_flag (KuiperLLama skips such a row silently, emb_kernel.cu:11-13).
+// out[t, :] = scale * table[ids[t], :] as float32 (scale 1 for a plain gather).  An id outside
+// [0, vocab) writes zeros and sets *error_flag (KuiperLLama skips such a row silently,
+// emb_kernel.cu:11-13).
 template <typename T>
 __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restrict__ table, float* __restrict__ out,
-                                 int hidden, int vocab, int* __restrict__ error_flag) {
+                                 int hidden, int vocab, float scale, int* __restrict__ error_flag) {
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
@@ -27,7 +28,7 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restric
         return;
     }
     const T* row = table + (size_t)id * hidden;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = to_f32(row[i]);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = scale * to_f32(row[i]);
 }
 
 // One CTA per output row r.  Source row s = rows ? rows[r] : r.
@@ -182,18 +183,42 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
     }
 }
 
+// Logits in place: x = scale * x, then, with a soft cap c > 0, x = c * tanh(x / c).
+__global__ void logit_transform_kernel(float* __restrict__ logits, long long ld, int rows, int vocab, float scale, float cap) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t n = (size_t)rows * vocab;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = idx / vocab;
+        float* p = logits + r * ld + (idx - r * vocab);
+        float x = *p * scale;
+        if (cap > 0.f) x = cap * tanhf(x / cap);
+        *p = x;
+    }
+}
+
 }  // namespace kl
 
 using namespace kl;
 
+KL_API int kl_logit_transform(float* logits, long long ld, int rows, int vocab, float scale, float softcap, cudaStream_t stream) {
+    if (rows <= 0 || vocab <= 0) return KL_OK;
+    if (softcap < 0.f || ld < vocab) return KL_ERR_BAD_SIZE;
+    const int threads = 256;
+    launch_kernel(logit_transform_kernel, kl::strided_grid((size_t)rows * vocab, threads, 16), threads, 0, stream, logits, ld, rows,
+                  vocab, scale, softcap);
+    KL_LAUNCH_CHECK();
+    return KL_OK;
+}
+
 KL_API int kl_embedding(const int* ids, int n_tokens, const void* table, int table_dtype, int vocab, int hidden,
-                        float* out, int* error_flag, cudaStream_t stream) {
+                        float scale, float* out, int* error_flag, cudaStream_t stream) {
     if (n_tokens <= 0) return KL_OK;
     const int threads = hidden >= 1024 ? 256 : 128;
     if (table_dtype == KL_F32)
-        launch_kernel(embedding_kernel<float>, n_tokens, threads, 0, stream, ids, (const float*)table, out, hidden, vocab, error_flag);
+        launch_kernel(embedding_kernel<float>, n_tokens, threads, 0, stream, ids, (const float*)table, out, hidden, vocab, scale, error_flag);
     else if (table_dtype == KL_BF16)
-        launch_kernel(embedding_kernel<bf16>, n_tokens, threads, 0, stream, ids, (const bf16*)table, out, hidden, vocab, error_flag);
+        launch_kernel(embedding_kernel<bf16>, n_tokens, threads, 0, stream, ids, (const bf16*)table, out, hidden, vocab, scale, error_flag);
     else
         return KL_ERR_BAD_DTYPE;
     KL_LAUNCH_CHECK();
@@ -226,7 +251,7 @@ KL_API int kl_swiglu(const void* gate_up, void* out, int tokens, int inter, int 
     if (tokens <= 0) return KL_OK;
     const size_t n = (size_t)tokens * inter;
     const int threads = 256;
-    const int blocks = (int)((n + threads - 1) / threads < 148 * 16 ? (n + threads - 1) / threads : 148 * 16);
+    const int blocks = kl::strided_grid(n, threads, 16);
     if (dtype == KL_F32)
         launch_kernel(swiglu_kernel<float>, blocks, threads, 0, stream, (const float*)gate_up, (float*)out, tokens, inter);
     else if (dtype == KL_BF16)

@@ -217,9 +217,40 @@ sample_rows_kernel(const float* __restrict__ logits, size_t row_stride, int voca
     }
 }
 
+// out[row] = log softmax(logits[row])[tokens[row]] = x[token] - max - log(sum exp(x - max)), in
+// float32; a token outside the vocabulary gives -inf.  (KuiperLLama's Python model has the same
+// softmax over the last position's logits, tools/model.py:327-339.)
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+token_logprob_kernel(const float* __restrict__ logits, size_t row_stride, int vocab, const int* __restrict__ tokens,
+                     float* __restrict__ out) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float scratch[33];
+    const float* x = logits + (size_t)blockIdx.x * row_stride;
+    float m = -INFINITY;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) m = fmaxf(m, x[i]);
+    m = block_max(m, scratch);
+    float s = 0.f;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) s += expf(x[i] - m);
+    s = block_sum(s, scratch);
+    if (threadIdx.x == 0) {
+        const int t = tokens[blockIdx.x];
+        out[blockIdx.x] = (t >= 0 && t < vocab) ? (x[t] - m) - logf(s) : -INFINITY;
+    }
+}
+
 }  // namespace kl
 
 using namespace kl;
+
+KL_API int kl_token_logprob(const float* logits, long long row_stride, int rows, int vocab, const int* tokens, float* out,
+                            cudaStream_t stream) {
+    if (rows <= 0) return KL_OK;
+    if (vocab <= 0) return KL_ERR_BAD_SIZE;
+    launch_kernel(token_logprob_kernel, rows, SAMPLE_THREADS, 0, stream, logits, (size_t)row_stride, vocab, tokens, out);
+    KL_LAUNCH_CHECK();
+    return KL_OK;
+}
 
 // Chunks a row is cut into by the two-stage argmax (the caller sizes scratch with it).
 KL_API int kl_argmax_chunks(int vocab) { return (vocab + ARGMAX_CHUNK - 1) / ARGMAX_CHUNK; }

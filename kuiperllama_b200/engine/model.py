@@ -36,10 +36,9 @@ def model_manifest(spec: ModelSpec) -> Dict[str, TensorDecl]:
 
 
 def ignorable_tensor_suffixes(spec: ModelSpec) -> Tuple[str, ...]:
-    """Names a checkpoint may hold without the model reading them: a classifier stored
-    beside a tied embedding table, and rotary tables that some exporters write."""
-    extra = ("rotary_emb.inv_freq",)
-    return extra + (("lm_head.weight",) if spec.lm_head_name is None else ())
+    """Name endings a checkpoint may hold without the model reading them; the architecture's
+    configuration lists them in its ``ModelSpec``."""
+    return tuple(spec.ignorable_suffixes)
 
 
 class DecoderModel:
@@ -55,7 +54,7 @@ class DecoderModel:
             self.lm_head = Linear(self.embedding, runtime)    # tied: the same storage, no copy
         else:
             self.lm_head = Linear(tensors[spec.lm_head_name], runtime)
-        self.error_flag = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.error_flag = ops.error_word(dev)               # shared per device; read with the status word in one copy
         # Option (bfloat16 decode steps of a few tokens): a block lets its products add into the residual
         # stream themselves and finish the norms in their epilogues (see parts/block.py).  It rounds
         # the normalised rows differently from the norm kernel (bf16(x * w) * r instead of
@@ -94,13 +93,21 @@ class DecoderModel:
                              dtype=self.runtime.dtype, device=self.runtime.device, max_slots=max_slots,
                              window_step_tokens=window_step_tokens)
 
+    def cache_bytes_per_token(self) -> int:
+        """Bytes of keys and values one token of one sequence takes over all executions that own
+        storage (per-slot state of fixed size is not counted)."""
+        kv, _, src = self.cache_requests()
+        esize = torch.empty(0, dtype=self.runtime.dtype).element_size()
+        return sum(2 * r.kv_heads * r.head_dim * esize for r, s in zip(kv, src) if r is not None and s is None)
+
     # ------------------------------------------------------------------ forward
     def hidden_states(self, step: StepContext, cache: SequenceCache) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
         """Run embedding and all scheduled layers: the float32 residual stream and the last
         feed-forward's output that is still to be added to it."""
         step.allow_stream_fusion = self.stream_fusion and step.is_decode
         residual = torch.empty((step.n_tokens, self.spec.hidden_size), dtype=torch.float32, device=self.runtime.device)
-        ops.embedding(step.token_ids[:step.n_tokens], self.embedding, residual, self.error_flag)
+        ops.embedding(step.token_ids[:step.n_tokens], self.embedding, residual, self.error_flag,
+                      scale=1.0 if self.spec.embedding_multiplier is None else float(self.spec.embedding_multiplier))
         first = self.blocks[self.spec.schedule[0].layer]
         if getattr(first, "position", None) is not None:
             first.position.add_to_embeddings(residual, step)
@@ -116,7 +123,11 @@ class DecoderModel:
     def logits(self, residual: torch.Tensor, pending: Optional[torch.Tensor], rows: torch.Tensor) -> torch.Tensor:
         """float32 logits [len(rows), vocab] of the given rows of the step."""
         x = self.final_norm.forward(residual, pending, rows.numel(), rows)
-        return self.lm_head.forward(x, out_dtype=torch.float32)
+        out = self.lm_head.forward(x, out_dtype=torch.float32)
+        if self.spec.logit_scale is not None or self.spec.logit_softcap is not None:
+            ops.logit_transform(out, 1.0 if self.spec.logit_scale is None else float(self.spec.logit_scale),
+                                float(self.spec.logit_softcap or 0.0))
+        return out
 
     def forward(self, step: StepContext, cache: SequenceCache, rows: torch.Tensor) -> torch.Tensor:
         residual, pending = self.hidden_states(step, cache)

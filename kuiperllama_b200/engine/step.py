@@ -262,7 +262,11 @@ class Engine:
         return g.logits
 
     def check_device_errors(self) -> None:
-        """Synchronises and raises if a kernel flagged a token id outside the vocabulary."""
-        if int(self.model.error_flag.item()):
-            self.model.error_flag.zero_()
-            raise StepError("a token id outside the vocabulary reached the embedding kernel")
+        """Synchronises, reads the device's two report words in one copy and raises if a kernel
+        gave up a bounded wait (``KernelError``: the step's results are not valid) or met a token
+        id outside the vocabulary (``StepError``).  What was set is cleared."""
+        from ..csrc import ops
+        try:
+            ops.check_device_words(self.device)
+        except ops.TokenIdError as e:
+            raise StepError(str(e)) from None

@@ -2,8 +2,9 @@
 model's parts declare.  One error lists every missing tensor, every unexpected tensor and
 every wrong shape or type.
 
-Storage rule: 16-bit floats are kept as bfloat16, a tensor stored in 32 bits stays float32,
-integer tables become int32.  (KuiperLLama has only float32 and finds tensors by offset,
+Storage rule: bfloat16 stays bfloat16, float16 stays float16 on the host (the parts round it
+once, to the run's compute dtype: exact in a float32 run), a tensor stored in 32 bits stays
+float32, integer tables become int32.  (KuiperLLama has only float32 and finds tensors by offset,
 kuiper/source/model/llama3.cpp:289-422, without a shape check, model.cpp:133-138.)
 """
 from __future__ import annotations
@@ -88,7 +89,7 @@ def stored_dtype(file_dtype: torch.dtype, role: str) -> Optional[torch.dtype]:
     if file_dtype not in _FLOATS:
         return None
     if file_dtype in (torch.float16, torch.bfloat16):
-        return torch.bfloat16
+        return file_dtype              # kept as stored; the parts convert once to the compute dtype
     return torch.float32
 
 
