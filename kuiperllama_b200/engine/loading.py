@@ -42,12 +42,15 @@ def load_model(folder: str, dtype="bfloat16", device="cuda:0") -> DecoderModel:
     return model
 
 
-def random_model(config, seed: int, dtype="bfloat16", device="cuda:0", std: float = 0.02) -> DecoderModel:
-    """A model with random weights made on the device (nothing is written)."""
+def random_model(config, seed: int, dtype="bfloat16", device="cuda:0", std: float = 0.02, stored=None) -> DecoderModel:
+    """A model with random weights made on the device (nothing is written).  ``stored``
+    ("bfloat16"): the values a checkpoint of that dtype would hold, so that a float32 model and a
+    bfloat16 model of one seed have the same weights."""
     device = require_cuda(device)
     spec = config.to_model_spec()
     dt = parse_dtype(dtype)
-    model = DecoderModel(spec, RandomTensors(model_manifest(spec), seed, device, dt, std), Runtime(device=device, dtype=dt))
+    tensors = RandomTensors(model_manifest(spec), seed, device, dt, std, stored=None if stored is None else parse_dtype(stored))
+    model = DecoderModel(spec, tensors, Runtime(device=device, dtype=dt))
     model.config = config
     return model
 

@@ -11,7 +11,7 @@ from __future__ import annotations
 import hashlib
 import json
 import os
-from typing import Dict, Iterator, Mapping
+from typing import Dict, Iterator, Mapping, Optional
 
 import torch
 
@@ -25,7 +25,9 @@ def _tensor_seed(seed: int, name: str) -> int:
 
 
 def random_tensor(name: str, decl: TensorDecl, seed: int, std: float, device="cpu",
-                  dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+                  dtype: torch.dtype = torch.bfloat16, stored: Optional[torch.dtype] = None) -> torch.Tensor:
+    """The tensor ``name`` for ``seed`` in ``dtype``.  With ``stored`` the values are first rounded
+    to that dtype, as a checkpoint of that dtype would hold them."""
     if decl.role == "int_table":
         raise ValueError(f"{name}: integer tables have no random initialisation")
     gen = torch.Generator(device=device)
@@ -35,6 +37,8 @@ def random_tensor(name: str, decl: TensorDecl, seed: int, std: float, device="cp
         t += 1.0
     elif decl.init != "normal":
         raise ValueError(f"{name}: unknown initialisation {decl.init!r}")
+    if stored is not None:
+        t = t.to(stored)
     return t.to(dtype)
 
 
@@ -52,14 +56,15 @@ class RandomTensors(Mapping):
     """``tensors[name]`` makes the tensor on ``device`` when it is asked for and keeps no
     copy: a model of any size can be built without a file."""
 
-    def __init__(self, manifest: Mapping[str, TensorDecl], seed: int, device, dtype: torch.dtype, std: float = 0.02):
-        self.manifest, self.seed, self.device, self.dtype, self.std = manifest, seed, device, dtype, std
+    def __init__(self, manifest: Mapping[str, TensorDecl], seed: int, device, dtype: torch.dtype, std: float = 0.02,
+                 stored: Optional[torch.dtype] = None):
+        self.manifest, self.seed, self.device, self.dtype, self.std, self.stored = manifest, seed, device, dtype, std, stored
 
     def __getitem__(self, name: str) -> torch.Tensor:
         decl = self.manifest[name]
         keep32 = decl.role == "vector"
         return random_tensor(name, decl, self.seed, self.std, device=self.device,
-                             dtype=torch.float32 if keep32 else self.dtype)
+                             dtype=torch.float32 if keep32 else self.dtype, stored=self.stored)
 
     def __iter__(self) -> Iterator[str]:
         return iter(self.manifest)

@@ -29,6 +29,19 @@ def pytest_collection_modifyitems(config, items):
             item.add_marker(skip)
 
 
+def pytest_terminal_summary(terminalreporter):
+    """The largest error of each dtype and configuration against the oracle, relative to the
+    oracle's largest logit: what the tolerances in helpers.py were set from."""
+    try:
+        from helpers import OBSERVED
+    except Exception:
+        return
+    if OBSERVED:
+        terminalreporter.write_line("largest observed error / largest reference magnitude:")
+        for (dtype, what), v in sorted(OBSERVED.items()):
+            terminalreporter.write_line(f"  {dtype:9s} {what:24s} {v:.3e}")
+
+
 @pytest.fixture(scope="session")
 def model_folders(tmp_path_factory):
     """Factory: folder of a tiny random model (written once per configuration and seed)."""

@@ -12,7 +12,9 @@ rotary table with theta 10000 and has no frequency scaling (tools/model.py:41,22
 ``freqs_cos`` / ``freqs_sin`` buffers are overwritten with our table, so for tiny2 theta and
 the llama3 scaling rule rest on the formulas alone, everything else on KuiperLLama's code.
 
-Writes tests/golden/<name>.pt: {"tokens", "logits" (float32 [T, vocab]), "weights_sha256"}.
+Writes tests/golden/<name>.pt: {"tokens", "logits" (float32 [T, vocab]), "weights" (the model's
+tensors as stored, bfloat16, so that the comparison does not depend on which random numbers a
+torch build draws), "weights_sha256"}.
 """
 import hashlib
 import importlib.util
@@ -99,7 +101,9 @@ def main():
         err = float((mine - theirs).abs().max())
         print(f"{name}: max |plain - KuiperLLama tools/model.py| = {err:.3e} (scale {float(theirs.abs().max()):.3e})")
         assert err < 2e-5 * float(theirs.abs().max()) + 1e-6
-        torch.save({"tokens": tokens, "logits": theirs, "weights_sha256": weights_digest(w)},
+        stored = {k: v.to(torch.bfloat16) for k, v in w.items()}
+        assert all(torch.equal(stored[k].float(), w[k]) for k in w)        # the folder holds bfloat16: nothing is lost
+        torch.save({"tokens": tokens, "logits": theirs, "weights": stored, "weights_sha256": weights_digest(w)},
                    os.path.join(HERE, f"{name}.pt"))
 
 

@@ -196,3 +196,58 @@ def test_a_windowed_group_can_have_a_smaller_pool():
         c.reserve(s, n + PAGE + 1)                          # more than the promised step
     c.free_slot(s)
     assert c.pages_held() == [0, 0]
+
+
+def test_a_cache_kind_can_be_registered_from_outside():
+    """Storage kinds are a registry like the parts: a kind defined here (a ring of one page per
+    slot that keeps only the newest keys) is built for the executions that ask for it, beside the
+    paged group of the others, and an unknown kind says which are known."""
+    from kuiperllama_b200.cache import register_cache_kind
+
+    @register_cache_kind("toy_last_page")
+    class LastPage:
+        def __init__(self, request, entries, n_pages, n_slots, blocks_per_seq, dtype, device, window_step_tokens=None):
+            self.request, self.entries = request, entries
+            self.k = torch.zeros((len(entries), n_slots, request.kv_heads, PAGE, request.head_dim), dtype=dtype, device=device)
+            self.v = torch.zeros_like(self.k)
+            self.table = torch.arange(n_slots, dtype=torch.int32, device=device).view(n_slots, 1)
+            self.live = set()
+            self.calls = []
+
+        def reserve(self, slot, old_length, new_length):
+            self.live.add(slot)
+            self.calls.append((slot, old_length, new_length))
+
+        def release(self, slot):
+            self.live.discard(slot)
+
+        def flush(self):
+            pass
+
+        def view(self, j):
+            return self.k[j], self.v[j], self.table
+
+        def held(self):
+            return len(self.live)
+
+        def pool_size(self):
+            return self.k.shape[1]
+
+        def bytes(self):
+            return 2 * self.k.numel() * self.k.element_size()
+
+    kv = [KVRequest(2, 16), KVRequest(2, 16, kind="toy_last_page"), KVRequest(2, 16)]
+    c = SequenceCache(kv, [None] * 3, [None] * 3, max_tokens=PAGE * 6, max_seq_len=PAGE * 3, dtype=torch.float32, device="cpu",
+                      max_slots=2)
+    kinds = {type(g).__name__: g for g in c.groups}
+    assert set(kinds) == {"PagedGroup", "LastPage"} and kinds["LastPage"].entries == [1]
+    s = c.alloc_slot()
+    c.reserve(s, 70)
+    c.flush_tables()
+    assert kinds["LastPage"].calls == [(s, 0, 70)] and sorted(c.pages_held()) == [1, 2]
+    assert tuple(c.view(1).k.shape) == (2, 2, PAGE, 16) and tuple(c.view(0).k.shape) == (6, 2, PAGE, 16)
+    c.free_slot(s)
+    assert c.pages_held() == [0, 0]
+    with pytest.raises(CacheError, match="toy_last_page"):          # the message lists the known kinds
+        SequenceCache([KVRequest(2, 16, kind="nothing_like_it")], [None], [None], max_tokens=PAGE, max_seq_len=PAGE,
+                      dtype=torch.float32, device="cpu")

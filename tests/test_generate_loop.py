@@ -130,3 +130,35 @@ def test_cache_limits_shape_the_batches():
     with pytest.raises(ValueError, match="no room"):
         run_requests(FakeBackend(1), [[1] * 64], 3, max_seq_len=64)
     assert run_requests(FakeBackend(1), [[1]], 0)[0].tokens == []
+
+
+def test_slots_are_handed_back_when_the_backend_raises():
+    """An exception inside a batch (here: the third decode step) leaves no slot held, so the same
+    cache serves the next call."""
+    class Failing(FakeBackend):
+        def decode(self, slots, previous, take, request_ids, steps):
+            if steps[0] == 3:
+                raise RuntimeError("the device said no")
+            return super().decode(slots, previous, take, request_ids, steps)
+
+    be = Failing(4)
+    with pytest.raises(RuntimeError, match="the device said no"):
+        run_requests(be, [[1, 2, 3], [4], [5, 6]], max_new_tokens=8, max_batch=4)
+    assert be.held == {} and sorted(be.free) == [0, 1, 2, 3]
+    ok = FakeBackend(4)
+    ok.free, ok.held = be.free, be.held
+    assert [len(r.tokens) for r in run_requests(ok, [[1, 2, 3], [4]], max_new_tokens=5, max_batch=4)] == [5, 5]
+
+
+def test_default_cache_size_fits_the_device_not_the_configuration():
+    """Llama 3.1's config.json says 131072 positions; 64 such sequences would be a terabyte of keys
+    and values.  The default is cut to a share of the memory that is free."""
+    from kuiperllama_b200.api import DEFAULT_CACHE_FRACTION, default_cache_tokens
+    per_token = 32 * 2 * 8 * 128 * 2                                  # Llama-3.1-8B in bfloat16: 128 KiB a token
+    free = 160 * 10**9
+    tokens = default_cache_tokens(per_token, max_batch=64, max_seq_len=131072, free_bytes=free)
+    assert tokens % PAGE == 0 and tokens * per_token <= DEFAULT_CACHE_FRACTION * free
+    assert tokens * per_token > 0.7 * free                             # and it does use what is there
+    # a small model keeps the size it asked for; no room at all still gives one page
+    assert default_cache_tokens(1024, max_batch=4, max_seq_len=100, free_bytes=free) == 4 * 2 * PAGE
+    assert default_cache_tokens(per_token, 64, 131072, free_bytes=1000) == PAGE

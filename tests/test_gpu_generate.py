@@ -52,6 +52,33 @@ def test_greedy_generation_through_the_entry_point(model_folders, name, seed, dt
     assert m.generate(prompts[0], max_new_tokens=3, stop_ids=[]) == out[0][:3]     # a single prompt, not nested
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_log_probabilities_and_logits_of_the_generated_tokens(model_folders, dtype):
+    """``return_logprobs`` / ``return_logits``: every new token comes with log softmax(logits)[token]
+    and with the logits row it was chosen from, also when batches shrink and graphs replay."""
+    import kuiperllama_b200 as kl
+    folder = model_folders("tiny2", seed=1)
+    vocab = config_dict("tiny2")["vocab_size"]
+    prompts = [random_tokens(n, vocab, seed=40 + n) for n in (6, 30, 2)]
+    m = kl.load(folder, dtype=dtype, max_tokens=64 * 6, max_batch=4)
+    out = m.generate(prompts, max_new_tokens=9, temperature=0.9, seed=3, stop_ids=[7], return_logprobs=True, return_logits=True)
+    results = m.last_results
+    assert out == m.generate(prompts, max_new_tokens=9, temperature=0.9, seed=3, stop_ids=[7])       # asking changes no token
+    c, w = plain_llama.read_config(folder), plain_llama.read_weights(folder)
+    assert len({len(o) for o in out}) > 1 or all(len(o) == 9 for o in out)
+    assert all(r.logprobs is None and r.logits is None for r in m.last_results)
+    for p, o, res in zip(prompts, out, results):
+        assert res.tokens == o and len(res.logprobs) == len(o) == len(res.logits)
+        ref = plain_llama.forward_logits(w, c, list(p) + o)[len(p) - 1:-1] if o else None
+        for i, tok in enumerate(o):
+            row = res.logits[i]
+            assert row.shape == (vocab,) and row.dtype == torch.float32
+            assert float((row - ref[i]).abs().max()) <= tolerance(dtype, ref[i])
+            want = float(torch.log_softmax(row.double(), dim=0)[tok])
+            assert abs(res.logprobs[i] - want) < 1e-4, (i, tok, res.logprobs[i], want)
+    assert m.cache.slots.held() == 0
+
+
 def test_stop_tokens_and_more_requests_than_the_cache_holds(model_folders):
     import kuiperllama_b200 as kl
     folder = model_folders("tiny2", seed=1)

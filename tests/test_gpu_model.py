@@ -272,6 +272,32 @@ def test_decode_steps_replayed_from_cuda_graphs(model_folders, name, dtype):
         ops.check_status(torch.device("cuda:0"))
 
 
+def test_a_float16_checkpoint_in_a_float32_run_keeps_its_values(tmp_path, model_folders):
+    """A folder stored in float16 (as Llama-2 checkpoints are): the float32 run uses exactly those
+    values, not values rounded to bfloat16 on the way; the bfloat16 run rounds them once."""
+    import shutil
+    from safetensors.torch import load_file, save_file
+    from kuiperllama_b200.engine import Engine, load_model
+    src = model_folders("tiny1", seed=0)
+    g = torch.Generator().manual_seed(5)
+    half = {k: (v.float() * (1 + 2.0 ** -10 * torch.randint(-3, 4, v.shape, generator=g))).half()
+            for k, v in load_file(f"{src}/model.safetensors").items()}      # values bfloat16 cannot hold
+    assert any(not torch.equal(v.bfloat16().half(), v) for v in half.values())
+    shutil.copy(f"{src}/config.json", tmp_path / "config.json")
+    save_file(half, str(tmp_path / "model.safetensors"))
+    tokens = random_tokens(40, config_dict("tiny1")["vocab_size"], seed=1300)
+    ref = plain_logits(str(tmp_path), tokens)                                # the oracle reads float16 as float32: exact
+    for dtype in DTYPES:
+        with torch.inference_mode():
+            model = load_model(str(tmp_path), dtype=dtype, device="cuda:0")
+            got = _whole(Engine(model, model.new_cache(max_tokens=64)), tokens)
+        assert_close(got, ref, dtype, f"tiny1 float16 checkpoint, {dtype} run")
+    rounded = {k: v.bfloat16().float() for k, v in half.items()}
+    import plain_llama
+    coarse = plain_llama.forward_logits(rounded, plain_llama.read_config(str(tmp_path)), tokens)
+    assert float((coarse - ref).abs().max()) > 20 * 2e-5 * float(ref.abs().max())   # the rounding the float32 run must not make is visible
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_llama31_8b_layer_sizes_one_layer(tmp_path_factory, dtype):
     """One layer with the widths of Llama-3.1-8B (hidden 4096, 32 heads, 8 kv heads, head size
@@ -299,6 +325,6 @@ def test_llama31_8b_layer_sizes_one_layer(tmp_path_factory, dtype):
         for t in tokens[140:]:
             got.append(engine.decode_step([slot], [t]).clone())
         engine.free_slot(slot)
-    assert_close(torch.cat(got), ref, dtype, f"8B-width layer, {dtype}")
+    assert_close(torch.cat(got), ref, dtype, f"8B-width layer, {dtype}", layers=1, stream="wide")
     from kuiperllama_b200.csrc import ops
     ops.check_status(torch.device("cuda:0"))

@@ -10,7 +10,7 @@ import pytest
 import torch
 
 import plain_llama
-from helpers import assert_close, config_dict, random_tokens
+from helpers import assert_close, config_dict, random_tokens, tolerance
 
 pytestmark = pytest.mark.gpu
 DEV = torch.device("cuda:0")
@@ -445,4 +445,39 @@ def test_layers_with_a_window_beside_layers_without(dtype):
             assert cache.pages_held() == [0, 0]
             for i in (0, 1):
                 ref = _windowed_reference(w, c, reqs[i], [W, None])
-                assert_close(torch.cat(got[i]), ref, dtype, f"window in layer 0, request {i}, round {round_}")
+                assert_close(torch.cat(got[i]), ref, dtype, f"window in layer 0, request {i}, round {round_}", layers=2, stream="wide")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_options_around_the_layers_embedding_multiplier_and_logit_scale_and_soft_cap(dtype):
+    """A ``ModelSpec`` may ask for x = m * E[token] and for logits = c * tanh(s * logits / c): steps
+    some decoders have around the layers and the Llama decoder has not.  They are fields of the
+    spec (None for Llama), not code of an architecture."""
+    from kuiperllama_b200.config import config_from_dict
+    from kuiperllama_b200.engine import DecoderModel, Engine, SequenceInput, model_manifest
+    from kuiperllama_b200.parts import Runtime
+    from kuiperllama_b200.weights.random_init import random_tensor
+    cfg = config_from_dict(config_dict("tiny3"))                    # untied: the classifier is not the embedding table
+    mult, scale, cap = math.sqrt(cfg.hidden_size), 4.0, 1.5
+    spec = dataclasses.replace(cfg.to_model_spec(), embedding_multiplier=mult, logit_scale=scale, logit_softcap=cap)
+    tensors = {n: random_tensor(n, d, seed=21, std=0.05) for n, d in model_manifest(spec).items()}
+    dt = DT[dtype]
+    model = DecoderModel(spec, tensors, Runtime(DEV, dt))
+    engine = Engine(model, model.new_cache(max_tokens=64 * 4))
+    w = {k: v.to(dt).float() for k, v in tensors.items()}
+    w["model.embed_tokens.weight"] = w["model.embed_tokens.weight"] * mult
+    tokens = random_tokens(90, cfg.vocab_size, seed=77)
+    raw = plain_llama.forward_logits(w, dict(config_dict("tiny3")), tokens)
+    ref = cap * torch.tanh(scale * raw / cap)
+    assert float(ref.abs().max()) > 0.5 * cap                       # the cap bites
+    with torch.inference_mode():
+        slot = engine.alloc_slot()
+        got = [engine.step([SequenceInput(slot, tokens[:60], list(range(60)))])]
+        got += [engine.step([SequenceInput(slot, [t], [0])]) for t in tokens[60:]]
+        engine.free_slot(slot)
+    got = torch.cat(got).float().cpu()
+    # tanh only shrinks differences, so the error after the cap is bounded by the error before it
+    assert float((got - ref).abs().max()) <= tolerance(dtype, scale * raw, layers=2, stream="wide")
+    assert float((got - ref).abs().max()) < 0.05 * float((got - scale * raw).abs().max())      # and the cap was applied
+    with pytest.raises(ValueError, match="logit_softcap"):
+        dataclasses.replace(spec, logit_softcap=0.0).validate()

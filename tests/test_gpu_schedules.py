@@ -1,0 +1,171 @@
+"""Schedules the step function allows beyond "prompts, then one token each", against the plain
+implementation in float32 and bfloat16, for a head size of 64 (tiny3) and of 128 (tiny4):
+
+* a prompt fed in several multi-token steps that cross page borders (a sequence that already
+  holds tokens brings more than one: both tensor-core prefill kernels with ``seq_starts > 0``);
+* a mixed step in which a fresh prompt joins sequences that are decoding;
+* decode steps replayed from CUDA graphs at 8, 20, 33 and 64 sequences (the 16-, 32- and
+  64-token tiles of the weights-as-rows products; decode attention with several pieces and with
+  one piece per sequence; its three-stage form at 64 sequences of 8 kv heads);
+* the option that folds the norms into the products at 3 and 4 sequences.
+"""
+from __future__ import annotations
+
+import pytest
+import torch
+
+from helpers import SEEDS, assert_close, config_dict, plain_logits, random_tokens
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = ["float32", "bfloat16"]
+CONFIGS = ["tiny3", "tiny4"]
+
+
+@pytest.fixture(scope="module")
+def models(model_folders):
+    from kuiperllama_b200.engine import load_model
+    made = {}
+
+    def get(name: str, dtype: str):
+        if (name, dtype) not in made:
+            folder = model_folders(name, seed=SEEDS[name])
+            with torch.inference_mode():
+                made[(name, dtype)] = (load_model(folder, dtype=dtype, device="cuda:0"), folder)
+        return made[(name, dtype)]
+
+    return get
+
+
+def _engine(model, max_tokens, use_graphs=False):
+    from kuiperllama_b200.engine import Engine
+    return Engine(model, model.new_cache(max_tokens=max_tokens), use_graphs=use_graphs)
+
+
+@pytest.mark.parametrize("prefill_kernel", ["tcgen05", "mma"])
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", CONFIGS)
+def test_a_prompt_in_several_multi_token_steps(models, name, dtype, prefill_kernel, monkeypatch):
+    """300 tokens as steps of 70, 130, 9 and 91 tokens: every step but the first starts inside a
+    page the sequence already holds part of, and ends in another."""
+    from kuiperllama_b200.csrc import ops
+    from kuiperllama_b200.engine import SequenceInput
+    if dtype == "float32" and prefill_kernel == "mma":
+        pytest.skip("the float32 path has one attention kernel")
+    monkeypatch.setattr(ops, "PREFILL_KERNEL", prefill_kernel)
+    model, folder = models(name, dtype)
+    engine = _engine(model, 64 * 8)
+    tokens = random_tokens(300, config_dict(name)["vocab_size"], seed=2100)
+    ref = plain_logits(folder, tokens)
+    got, start = [], 0
+    with torch.inference_mode():
+        slot = engine.alloc_slot()
+        for n in (70, 130, 9, 91):
+            got.append(engine.step([SequenceInput(slot, tokens[start:start + n], list(range(n)))]))
+            assert_close(got[-1], ref[start:start + n], dtype, f"{name} {prefill_kernel}: the step of {n} tokens from {start}")
+            start += n
+        engine.free_slot(slot)
+    engine.check_device_errors()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", CONFIGS)
+def test_a_fresh_prompt_joins_decoding_sequences(models, name, dtype):
+    """Two sequences are decoding; a step brings one token for each of them and a whole prompt of a
+    third (and later of a fourth, a single token long); then all decode together."""
+    from kuiperllama_b200.engine import SequenceInput
+    model, folder = models(name, dtype)
+    engine = _engine(model, 64 * 12)
+    vocab = config_dict(name)["vocab_size"]
+    reqs = [random_tokens(n, vocab, seed=2200 + n) for n in (90, 41, 77, 30)]
+    ref = [plain_logits(folder, r) for r in reqs]
+    done = [0, 0, 0, 0]
+    got = [[] for _ in reqs]
+    slots = {}
+
+    def step(parts):                                    # parts: {request: number of tokens it brings}
+        inputs = []
+        for i, n in parts.items():
+            if i not in slots:
+                slots[i] = engine.alloc_slot()
+            inputs.append(SequenceInput(slots[i], reqs[i][done[i]:done[i] + n], list(range(n))))
+        logits = engine.step(inputs)
+        o = 0
+        for i, n in parts.items():
+            got[i].append(logits[o:o + n])
+            o += n
+            done[i] += n
+
+    with torch.inference_mode():
+        step({0: 60, 1: 20})
+        step({0: 1, 1: 1})
+        step({0: 1, 1: 1, 2: 37})                       # the mixed step: a prompt of 37 joins
+        step({0: 1, 1: 1, 2: 1})
+        step({2: 1, 3: 1, 0: 1, 1: 1})                  # a prompt of one token joins, in another order
+        while any(done[i] < len(reqs[i]) for i in range(4)):
+            live = {i: 1 for i in range(4) if done[i] < len(reqs[i])}
+            step(live)
+            for i in list(slots):
+                if done[i] == len(reqs[i]):
+                    engine.free_slot(slots.pop(i))
+    for i in range(4):
+        assert_close(torch.cat(got[i]), ref[i], dtype, f"{name} request {i} of the mixed schedule")
+    assert engine.cache.slots.held() == 0 and engine.cache.pages_held() == [0]
+    engine.check_device_errors()
+
+
+@pytest.mark.parametrize("batch", [8, 20, 33, 64])
+@pytest.mark.parametrize("name", CONFIGS)
+def test_graph_decode_at_larger_batches(models, name, batch):
+    """bfloat16 decode steps replayed from a CUDA graph at batch sizes that take the 16-, 32- and
+    64-token tiles of the products and every form of the decode attention; the same steps
+    without a graph give the same bits, and both agree with the plain implementation."""
+    from kuiperllama_b200.engine import SequenceInput
+    model, folder = models(name, "bfloat16")
+    vocab = config_dict(name)["vocab_size"]
+    steps = 5
+    reqs = [random_tokens(3 + (i * 11) % 70 + steps, vocab, seed=2300 + i) for i in range(batch)]
+    outs = {}
+    for use_graphs in (False, True):
+        engine = _engine(model, 64 * 2 * batch, use_graphs=use_graphs)
+        with torch.inference_mode():
+            slots = [engine.alloc_slot() for _ in reqs]
+            engine.step([SequenceInput(s, r[:-steps], []) for s, r in zip(slots, reqs)])
+            rows = []
+            for k in range(steps):
+                rows.append(engine.decode_step(slots, [r[len(r) - steps + k] for r in reqs]).clone())
+            for s in slots:
+                engine.free_slot(s)
+        outs[use_graphs] = torch.stack(rows, dim=1)          # [batch, steps, vocab]
+        assert (sorted(engine._graphs) == [batch]) == use_graphs
+        engine.check_device_errors()
+    assert torch.equal(outs[True], outs[False]), "a replayed graph gave other logits than the same kernels launched one by one"
+    for i in sorted({0, 1, batch // 2, batch - 2, batch - 1}):
+        assert_close(outs[True][i], plain_logits(folder, reqs[i])[-steps:], "bfloat16", f"{name} graph decode, sequence {i} of {batch}")
+
+
+@pytest.mark.parametrize("n_seqs", [3, 4])
+@pytest.mark.parametrize("name", CONFIGS)
+def test_stream_fusion_at_three_and_four_sequences(models, model_folders, name, n_seqs):
+    from kuiperllama_b200.csrc import ops
+    from kuiperllama_b200.engine import SequenceInput, load_model
+    folder = model_folders(name, seed=SEEDS[name])
+    vocab = config_dict(name)["vocab_size"]
+    steps = 12
+    reqs = [random_tokens(20 + 13 * i + steps, vocab, seed=2400 + i) for i in range(n_seqs)]
+    launches = {}
+    for fusion in (False, True):
+        with torch.inference_mode():
+            model = load_model(folder, dtype="bfloat16", device="cuda:0")
+            model.stream_fusion = fusion
+            engine = _engine(model, 64 * 2 * n_seqs)
+            slots = [engine.alloc_slot() for _ in reqs]
+            engine.step([SequenceInput(s, r[:-steps], []) for s, r in zip(slots, reqs)])
+            before = ops.launch_count
+            rows = [engine.step([SequenceInput(s, [r[len(r) - steps + k]], [0]) for s, r in zip(slots, reqs)]) for k in range(steps)]
+            launches[fusion] = ops.launch_count - before
+        got = torch.stack(rows, dim=1)
+        for i, r in enumerate(reqs):
+            assert_close(got[i], plain_logits(folder, r)[-steps:], "bfloat16", f"{name} stream fusion {fusion}, {n_seqs} sequences")
+        engine.check_device_errors()
+    assert launches[True] < launches[False], launches
