@@ -16,6 +16,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence, Tuple
 
+import numpy as np
 import torch
 
 from ..cache import PAGE, CacheError, SequenceCache
@@ -53,13 +54,21 @@ class _Staging:
         self.turn = 0
         self.dev = torch.zeros(capacity, dtype=torch.int32, device=device)
 
-    def upload(self, flat: List[int]) -> torch.Tensor:
+    def upload(self, flat) -> torch.Tensor:
+        """``flat``: a list of ints, or a list of int32 numpy arrays that are laid end to end."""
         i = self.turn
         self.turn = (i + 1) % self.RING
         if self.used[i] and self.events[i] is not None:
             self.events[i].synchronize()
-        n = len(flat)
-        self.hosts[i][:n] = torch.tensor(flat, dtype=torch.int32)
+        if flat and isinstance(flat[0], np.ndarray):
+            view = self.hosts[i].numpy()
+            n = 0
+            for a in flat:
+                view[n:n + a.size] = a
+                n += a.size
+        else:
+            n = len(flat)
+            self.hosts[i][:n] = torch.tensor(flat, dtype=torch.int32)
         self.dev[:n].copy_(self.hosts[i][:n], non_blocking=True)
         if self.events[i] is not None:
             self.events[i].record()
@@ -97,7 +106,7 @@ class Engine:
         if not inputs:
             raise StepError("an empty batch")
         vocab = self.model.spec.vocab_size
-        slots, starts, news = [], [], []
+        slots, starts, news, token_arrays = [], [], [], []
         seen = set()
         for s in inputs:
             if not self.cache.slots.is_held(s.slot):
@@ -111,9 +120,11 @@ class Engine:
             for w in s.want:
                 if not 0 <= w < n:
                     raise StepError(f"slot {s.slot}: wanted place {w} is outside its {n} tokens")
-            lo, hi = min(s.tokens), max(s.tokens)
+            toks = np.asarray(s.tokens, dtype=np.int64)
+            lo, hi = int(toks.min()), int(toks.max())
             if lo < 0 or hi >= vocab:
                 raise StepError(f"slot {s.slot}: token id {lo if lo < 0 else hi} is outside the vocabulary of {vocab}")
+            token_arrays.append(toks.astype(np.int32))
             slots.append(s.slot)
             starts.append(self.cache.lengths[s.slot])
             news.append(n)
@@ -132,19 +143,15 @@ class Engine:
         total = 3 * n_rows + 3 * n_seqs + (n_seqs + 1) + n_want
         if self._staging is None or self._staging.capacity < total:
             self._staging = _Staging(max(total * 2, 1 << 16), self.device)
-        ids, pos, tsl, cu, want = [], [], [], [0], []
-        row = 0
-        for s, st, n in zip(inputs, starts, news):
-            ids.extend(int(t) for t in s.tokens)
-            pos.extend(range(st, st + n))
-            tsl.extend([s.slot] * n)
-            want.extend(row + w for w in s.want)
-            row += n
-            cu.append(row)
-        ids.extend([0] * pad_rows)
-        pos.extend([0] * pad_rows)
-        tsl.extend([-1] * pad_rows)
-        flat = ids + pos + tsl + slots + starts + news + cu + want
+        i32 = np.int32
+        pad = np.zeros(pad_rows, dtype=i32)
+        cu = np.zeros(n_seqs + 1, dtype=i32)
+        np.cumsum(news, out=cu[1:])
+        want = [cu[j] + np.asarray(s.want, dtype=i32) for j, s in enumerate(inputs) if len(s.want)]
+        flat = (token_arrays + [pad]
+                + [np.arange(st, st + n, dtype=i32) for st, n in zip(starts, news)] + [pad]
+                + [np.full(n, sl, dtype=i32) for sl, n in zip(slots, news)] + [np.full(pad_rows, -1, dtype=i32)]
+                + [np.asarray(slots, dtype=i32), np.asarray(starts, dtype=i32), np.asarray(news, dtype=i32), cu] + want)
         d = self._staging.upload(flat)
         o = 0
 

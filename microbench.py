@@ -1,11 +1,11 @@
 """Time one kernel of the package alone on synthetic operands (CUDA events, median of
 repeats, a buffer larger than L2 written between repeats), and print the achieved rate.
 
-    python -m kuiperllama_b200.csrc.microbench gemm_skinny --m 8 --n 28672 --k 4096 [--swiglu]
-    python -m kuiperllama_b200.csrc.microbench gemm_tcgen05 --m 2048 --n 6144 --k 4096
-    python -m kuiperllama_b200.csrc.microbench attention_prefill --tokens 2048 --heads 32 --kv-heads 8 --head-dim 128 [--mma]
-    python -m kuiperllama_b200.csrc.microbench attention_decode --batch 64 --context 640 --heads 32 --kv-heads 8 --head-dim 128
-    python -m kuiperllama_b200.csrc.microbench attention_decode --batch 8 --context 516 --fused     (the decode step's form)
+    python microbench.py gemm_skinny --m 8 --n 28672 --k 4096 [--swiglu]
+    python microbench.py gemm_tcgen05 --m 2048 --n 6144 --k 4096
+    python microbench.py attention_prefill --tokens 2048 --heads 32 --kv-heads 8 --head-dim 128 [--mma]
+    python microbench.py attention_decode --batch 64 --context 640 --heads 32 --kv-heads 8 --head-dim 128
+    python microbench.py attention_decode --batch 8 --context 516 --fused     (the decode step's form)
 
 It is also the small case that profiler captures of single kernels are taken on.
 """
@@ -14,11 +14,13 @@ from __future__ import annotations
 import argparse
 import json
 import math
+import os
 import sys
 
 import torch
 
-from . import ops
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+from kuiperllama_b200.csrc import ops  # noqa: E402
 
 DEV = torch.device("cuda:0")
 

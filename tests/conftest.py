@@ -48,11 +48,11 @@ def model_folders(tmp_path_factory):
     from helpers import write_folder
     made = {}
 
-    def get(name: str, seed: int = 0, **overrides) -> str:
-        key = (name, seed, tuple(sorted(overrides.items())))
+    def get(name: str, seed: int = 0, std: float = 0.02, **overrides) -> str:
+        key = (name, seed, std, tuple(sorted(overrides.items())))
         if key not in made:
             folder = str(tmp_path_factory.mktemp(f"{name}-s{seed}"))
-            write_folder(folder, name, seed, **overrides)
+            write_folder(folder, name, seed, std=std, **overrides)
             made[key] = folder
         return made[key]
 

@@ -53,11 +53,13 @@ def config_dict(name: str, **overrides) -> dict:
     return d
 
 
-def write_folder(folder: str, name: str, seed: int, **overrides) -> None:
-    """A model folder of random weights through the package's random-weights mode."""
+def write_folder(folder: str, name: str, seed: int, std: float = 0.02, **overrides) -> None:
+    """A model folder of random weights through the package's random-weights mode.  ``std`` 0.02
+    is the workloads' figure; with 0.08 the scores of the tiny models spread over several units, so
+    that the softmax has sharp peaks and a wrong scale, mask, position or page shows in the logits."""
     from kuiperllama_b200.config import config_from_dict
     from kuiperllama_b200.engine import write_random_model_folder
-    write_random_model_folder(folder, config_from_dict(config_dict(name, **overrides)), seed)
+    write_random_model_folder(folder, config_from_dict(config_dict(name, **overrides)), seed, std=std)
 
 
 def random_tokens(n: int, vocab: int, seed: int) -> List[int]:

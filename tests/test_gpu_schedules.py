@@ -8,6 +8,8 @@ implementation in float32 and bfloat16, for a head size of 64 (tiny3) and of 128
   64-token tiles of the weights-as-rows products; decode attention with several pieces and with
   one piece per sequence; its three-stage form at 64 sequences of 8 kv heads);
 * the option that folds the norms into the products at 3 and 4 sequences.
+
+The models here have weights N(0, 0.08), see ``SHARP``.
 """
 from __future__ import annotations
 
@@ -20,6 +22,10 @@ pytestmark = pytest.mark.gpu
 
 DTYPES = ["float32", "bfloat16"]
 CONFIGS = ["tiny3", "tiny4"]
+# Weights N(0, 0.08) instead of N(0, 0.02): scores spread over several units, the softmax has sharp
+# peaks, and a wrong scale, mask, position or page moves the logits far beyond the tolerance.
+SHARP = 0.08
+WIDE = dict(layers=2, stream="wide")
 
 
 @pytest.fixture(scope="module")
@@ -29,7 +35,7 @@ def models(model_folders):
 
     def get(name: str, dtype: str):
         if (name, dtype) not in made:
-            folder = model_folders(name, seed=SEEDS[name])
+            folder = model_folders(name, seed=SEEDS[name], std=SHARP)
             with torch.inference_mode():
                 made[(name, dtype)] = (load_model(folder, dtype=dtype, device="cuda:0"), folder)
         return made[(name, dtype)]
@@ -62,7 +68,7 @@ def test_a_prompt_in_several_multi_token_steps(models, name, dtype, prefill_kern
         slot = engine.alloc_slot()
         for n in (70, 130, 9, 91):
             got.append(engine.step([SequenceInput(slot, tokens[start:start + n], list(range(n)))]))
-            assert_close(got[-1], ref[start:start + n], dtype, f"{name} {prefill_kernel}: the step of {n} tokens from {start}")
+            assert_close(got[-1], ref[start:start + n], dtype, f"{name} {prefill_kernel}: the step of {n} tokens from {start}", **WIDE)
             start += n
         engine.free_slot(slot)
     engine.check_device_errors()
@@ -109,7 +115,7 @@ def test_a_fresh_prompt_joins_decoding_sequences(models, name, dtype):
                 if done[i] == len(reqs[i]):
                     engine.free_slot(slots.pop(i))
     for i in range(4):
-        assert_close(torch.cat(got[i]), ref[i], dtype, f"{name} request {i} of the mixed schedule")
+        assert_close(torch.cat(got[i]), ref[i], dtype, f"{name} request {i} of the mixed schedule", **WIDE)
     assert engine.cache.slots.held() == 0 and engine.cache.pages_held() == [0]
     engine.check_device_errors()
 
@@ -141,7 +147,7 @@ def test_graph_decode_at_larger_batches(models, name, batch):
         engine.check_device_errors()
     assert torch.equal(outs[True], outs[False]), "a replayed graph gave other logits than the same kernels launched one by one"
     for i in sorted({0, 1, batch // 2, batch - 2, batch - 1}):
-        assert_close(outs[True][i], plain_logits(folder, reqs[i])[-steps:], "bfloat16", f"{name} graph decode, sequence {i} of {batch}")
+        assert_close(outs[True][i], plain_logits(folder, reqs[i])[-steps:], "bfloat16", f"{name} graph decode, sequence {i} of {batch}", **WIDE)
 
 
 @pytest.mark.parametrize("n_seqs", [3, 4])
@@ -149,7 +155,7 @@ def test_graph_decode_at_larger_batches(models, name, batch):
 def test_stream_fusion_at_three_and_four_sequences(models, model_folders, name, n_seqs):
     from kuiperllama_b200.csrc import ops
     from kuiperllama_b200.engine import SequenceInput, load_model
-    folder = model_folders(name, seed=SEEDS[name])
+    folder = model_folders(name, seed=SEEDS[name], std=SHARP)
     vocab = config_dict(name)["vocab_size"]
     steps = 12
     reqs = [random_tokens(20 + 13 * i + steps, vocab, seed=2400 + i) for i in range(n_seqs)]
@@ -166,6 +172,6 @@ def test_stream_fusion_at_three_and_four_sequences(models, model_folders, name, 
             launches[fusion] = ops.launch_count - before
         got = torch.stack(rows, dim=1)
         for i, r in enumerate(reqs):
-            assert_close(got[i], plain_logits(folder, r)[-steps:], "bfloat16", f"{name} stream fusion {fusion}, {n_seqs} sequences")
+            assert_close(got[i], plain_logits(folder, r)[-steps:], "bfloat16", f"{name} stream fusion {fusion}, {n_seqs} sequences", **WIDE)
         engine.check_device_errors()
     assert launches[True] < launches[False], launches
