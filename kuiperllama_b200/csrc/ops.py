@@ -628,7 +628,9 @@ def attention_tcgen05(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache
         "attention_tcgen05")
 
 
-# Which kernel prefill steps of the bfloat16 path use for head sizes 64 and 128: "tcgen05" or "mma".
+# Which kernel prefill steps of the bfloat16 path use for head sizes 64 and 128: "tcgen05", or "mma"
+# (the kernel that serves windows and other group sizes).  Kept as a switch so that tests can run
+# whole models through the second kernel too (tests/test_gpu_schedules.py).
 PREFILL_KERNEL = "tcgen05"
 
 _counters: Dict[tuple, torch.Tensor] = {}
@@ -703,7 +705,7 @@ def attention_decode_fused(qkv: torch.Tensor, inv_freq: torch.Tensor, out: torch
 
 
 # Which kernel decode steps of the bfloat16 path use when both fit: "mma" (tensor cores) or
-# "simt" (attention_decode.cu).
+# "simt" (attention_decode.cu, which otherwise serves head sizes 16, 32 and 256); a switch for tests.
 DECODE_KERNEL = "mma"
 
 

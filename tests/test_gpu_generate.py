@@ -161,3 +161,23 @@ def test_command_line(model_folders):
     assert len(first) <= 11 and first == plain_llama.greedy_generate(w, c, [1, 5, 9, 200], 11, stop_ids=[2])[:len(first)]
     bad = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "llama_infer"), folder], capture_output=True, text=True, timeout=600)
     assert bad.returncode != 0 and "tokenizer" in bad.stderr
+
+
+def test_per_kernel_timing_of_a_generation(model_folders):
+    """``profiling.kernel_timing``: every kernel entry point between two CUDA events, summed by name."""
+    import kuiperllama_b200 as kl
+    from kuiperllama_b200 import profiling
+    from kuiperllama_b200.csrc import ops
+    folder = model_folders("tiny3", seed=2)
+    m = kl.load(folder, dtype="bfloat16", max_tokens=64 * 4, max_batch=2, use_graphs=False)
+    prompts = [random_tokens(n, config_dict("tiny3")["vocab_size"], seed=n) for n in (40, 9)]
+    plain = m.generate(prompts, max_new_tokens=5, stop_ids=[])
+    before = ops.gemm_skinny
+    with profiling.kernel_timing() as times:
+        assert m.generate(prompts, max_new_tokens=5, stop_ids=[]) == plain           # timing changes no token
+    assert ops.gemm_skinny is before                                                 # the entry points are back
+    totals = times.totals()
+    assert totals["embedding"][0] == 5 and totals["argmax_rows"][0] == 5             # one prefill and four decode steps
+    assert totals["attention_tcgen05"][0] == 2 and totals["attention_decode_fused"][0] == 2 * 4
+    assert all(ms > 0 for _, ms in totals.values())
+    assert "total over" in times.report()
