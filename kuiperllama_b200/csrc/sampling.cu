@@ -124,23 +124,30 @@ __device__ __forceinline__ float uniform_from_counter(unsigned long long seed, u
     return (float)(z >> 40) * (1.0f / 16777216.0f);
 }
 
-__device__ __forceinline__ int block_count(int v, int* scratch) {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-    __syncthreads();
-    if (lane == 0) scratch[warp] = v;
-    __syncthreads();
-    if (warp == 0) {
-        int t = lane < nwarps ? scratch[lane] : 0;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
-        if (lane == 0) scratch[32] = t;
-    }
-    __syncthreads();
-    return scratch[32];
+// Four consecutive logits of a row starting at element i (a multiple of 4); elements past the
+// vocabulary read as -inf.  `vec`: the row starts on a 16-byte boundary, so one load does it.
+__device__ __forceinline__ float4 load4(const float* __restrict__ x, int i, int vocab, bool vec) {
+    if (vec && i + 3 < vocab) return *reinterpret_cast<const float4*>(x + i);
+    float4 v;
+    v.x = i < vocab ? x[i] : -INFINITY;
+    v.y = i + 1 < vocab ? x[i + 1] : -INFINITY;
+    v.z = i + 2 < vocab ? x[i + 2] : -INFINITY;
+    v.w = i + 3 < vocab ? x[i + 3] : -INFINITY;
+    return v;
 }
 
+constexpr int SAMPLE_TILE = SAMPLE_THREADS * 4;       // logits a CTA reads per pass over its threads
+constexpr int SAMPLE_MAX_TILES = 256;                 // rows of up to 2^20 logits
+
+// One CTA per row.  Every pass reads the row in tiles of 4,096 consecutive logits, thread t taking
+// the four at 4 t, so that loads are coalesced and a warp owns 128 consecutive logits of a tile:
+//   1. with top-k, the k-th largest logit as an ordered key, by four passes of an 8-bit radix
+//      select over shared-memory histograms;
+//   2. the maximum;
+//   3. sum of exp((x - max) / T) over the kept logits per (tile, warp), then per tile and in all,
+//      added in index order in float64;
+//   4. the (tile, warp) whose stretch of the cumulative sum holds u * total, and inside that warp
+//      the first logit at which the running sum passes it.
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_rows_kernel(const float* __restrict__ logits, size_t row_stride, int vocab, float temperature, int top_k,
                    unsigned long long seed, const int* __restrict__ request_ids, const int* __restrict__ steps,
@@ -148,73 +155,147 @@ sample_rows_kernel(const float* __restrict__ logits, size_t row_stride, int voca
     pdl_launch_dependents();
     pdl_wait();
     __shared__ float fscratch[33];
-    __shared__ int iscratch[33];
-    __shared__ double part[SAMPLE_THREADS];
-    __shared__ int chosen;
-    __shared__ double total_s;
-    const int row = blockIdx.x;
+    __shared__ unsigned int hist[256];
+    __shared__ unsigned int sel_prefix, sel_remaining;
+    __shared__ float warp_sums[SAMPLE_MAX_TILES][32];
+    __shared__ double tile_sums[SAMPLE_MAX_TILES];
+    __shared__ int pick_tile, pick_warp, pick_last, chosen;
+    __shared__ double pick_base, pick_target;
+    const int row = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const float* x = logits + (size_t)row * row_stride;
+    const bool vec = (((uintptr_t)x) & 15) == 0;
     const float inv_t = 1.0f / temperature;
+    const int n_tiles = (vocab + SAMPLE_TILE - 1) / SAMPLE_TILE;
 
-    // threshold of the top-k cut as an ordered key; 0 keeps everything
+    // 1. threshold of the top-k cut as an ordered key; 0 keeps everything
     unsigned int th = 0u;
     if (top_k > 0 && top_k < vocab) {
-        // the largest key K with count(key >= K) >= top_k, bit by bit from the top
-        unsigned int k = 0u;
-        for (int bit = 31; bit >= 0; --bit) {
-            const unsigned int trial = k | (1u << bit);
-            int c = 0;
-            for (int i = threadIdx.x; i < vocab; i += blockDim.x) c += ordered_key(x[i]) >= trial;
-            if (block_count(c, iscratch) >= top_k) k = trial;
+        if (threadIdx.x == 0) { sel_prefix = 0u; sel_remaining = (unsigned int)top_k; }
+        for (int shift = 24; shift >= 0; shift -= 8) {
+            if (threadIdx.x < 256) hist[threadIdx.x] = 0u;
+            __syncthreads();
+            const unsigned int prefix = sel_prefix;
+            const unsigned int mask = shift == 24 ? 0u : (0xffffffffu << (shift + 8));
+            for (int t = 0; t < n_tiles; ++t) {
+                const int i = t * SAMPLE_TILE + threadIdx.x * 4;
+                const float4 v = load4(x, i, vocab, vec);
+                const float e[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const unsigned int key = ordered_key(e[j]);
+                    if (i + j < vocab && (key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 255u], 1u);
+                }
+            }
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                // the bin that holds the k-th largest among the keys with this prefix, from the top
+                unsigned int remaining = sel_remaining, b = 255u;
+                for (;; --b) {
+                    if (hist[b] >= remaining || b == 0u) break;
+                    remaining -= hist[b];
+                }
+                sel_prefix = prefix | (b << shift);
+                sel_remaining = remaining;
+            }
+            __syncthreads();
         }
-        th = k;
+        th = sel_prefix;
     }
+
+    // 2. the maximum (the largest logit is always kept)
     float m = -INFINITY;
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) m = fmaxf(m, x[i]);
+    for (int t = 0; t < n_tiles; ++t) {
+        const float4 v = load4(x, t * SAMPLE_TILE + threadIdx.x * 4, vocab, vec);
+        m = fmaxf(fmaxf(m, fmaxf(v.x, v.y)), fmaxf(v.z, v.w));
+    }
     m = block_max(m, fscratch) * inv_t;
 
-    // every thread owns one contiguous segment, so the cumulative sum runs in index order
-    const int per = (vocab + blockDim.x - 1) / blockDim.x;
-    const int begin = min(threadIdx.x * per, vocab), end = min(begin + per, vocab);
-    double s = 0.0;
-    for (int i = begin; i < end; ++i)
-        if (ordered_key(x[i]) >= th) s += (double)expf(x[i] * inv_t - m);
-    part[threadIdx.x] = s;
+    // 3. sums per (tile, warp)
+    auto weight = [&](float v, int i) -> float {
+        return (i < vocab && ordered_key(v) >= th) ? expf(v * inv_t - m) : 0.f;
+    };
+    for (int t = 0; t < n_tiles; ++t) {
+        const int i = t * SAMPLE_TILE + threadIdx.x * 4;
+        const float4 v = load4(x, i, vocab, vec);
+        float s = (weight(v.x, i) + weight(v.y, i + 1)) + (weight(v.z, i + 2) + weight(v.w, i + 3));
+        s = warp_sum(s);
+        if (lane == 0) warp_sums[t][warp] = s;
+    }
     if (threadIdx.x == 0) chosen = -1;
     __syncthreads();
-    if (threadIdx.x == 0) {                                  // exclusive scan of 1024 partial sums
-        double run = 0.0;
-        for (int i = 0; i < blockDim.x; ++i) { const double p = part[i]; part[i] = run; run += p; }
-        part[0] = 0.0;
-        total_s = run;
+    if (threadIdx.x < n_tiles) {
+        double s = 0.0;
+        for (int w = 0; w < 32; ++w) s += (double)warp_sums[threadIdx.x][w];
+        tile_sums[threadIdx.x] = s;
     }
     __syncthreads();
-    const double total = total_s;
-    const double target = (double)uniform_from_counter(seed, (unsigned long long)request_ids[row],
-                                                       (unsigned long long)steps[row]) * total;
-    const double excl = part[threadIdx.x];
-    if (s > 0.0 && excl <= target && target < excl + s) {
-        double run = excl;
-        int pick = -1, last_kept = -1;
-        for (int i = begin; i < end && pick < 0; ++i) {
-            if (ordered_key(x[i]) >= th) {
-                last_kept = i;
-                run += (double)expf(x[i] * inv_t - m);
-                if (run > target) pick = i;
+
+    // 4. where u * total falls
+    if (threadIdx.x == 0) {
+        double total = 0.0;
+        for (int t = 0; t < n_tiles; ++t) total += tile_sums[t];
+        const double target = (double)uniform_from_counter(seed, (unsigned long long)request_ids[row],
+                                                           (unsigned long long)steps[row]) * total;
+        double run = 0.0;
+        int pt = -1, pw = -1;
+        for (int t = 0; t < n_tiles && pt < 0; ++t) {
+            if (tile_sums[t] > 0.0 && target < run + tile_sums[t]) {
+                for (int w = 0; w < 32 && pw < 0; ++w) {
+                    const double s = (double)warp_sums[t][w];
+                    if (s > 0.0 && target < run + s) pw = w;
+                    else run += s;
+                }
+                if (pw >= 0) pt = t;
+                // else rounding: the warp sums of this tile end below the target; go on with the next tile
+            } else {
+                run += tile_sums[t];
             }
         }
-        chosen = pick >= 0 ? pick : last_kept;
+        int last = 0;
+        if (pt < 0) {                                       // rounding put the target past the end: the last kept logit of all
+            last = 1;
+            for (int t = n_tiles - 1; t >= 0 && pt < 0; --t)
+                for (int w = 31; w >= 0 && pt < 0; --w)
+                    if (warp_sums[t][w] > 0.f) { pt = t; pw = w; }
+            if (pt < 0) { pt = 0; pw = 0; }
+        }
+        pick_tile = pt; pick_warp = pw; pick_base = run; pick_target = target; pick_last = last;
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
-        int c = chosen;
-        if (c < 0) {                                         // rounding put the target past the end: last kept token
-            for (int i = vocab - 1; i >= 0 && c < 0; --i)
-                if (ordered_key(x[i]) >= th && expf(x[i] * inv_t - m) > 0.f) c = i;
-            if (c < 0) c = 0;
+    if (warp == pick_warp) {
+        const double target = pick_target;
+        const int i = pick_tile * SAMPLE_TILE + threadIdx.x * 4;
+        const float4 v = load4(x, i, vocab, vec);
+        const float e[4] = {weight(v.x, i), weight(v.y, i + 1), weight(v.z, i + 2), weight(v.w, i + 3)};
+        // inclusive running sums in index order: lanes in order, four logits inside a lane
+        double mine = ((double)e[0] + (double)e[1]) + ((double)e[2] + (double)e[3]);
+        double incl = mine;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const double other = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += other;
         }
-        out[row] = c;
+        double run = pick_base + (incl - mine);
+        int pick = -1, last_kept = -1;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            if (e[j] > 0.f) {
+                last_kept = i + j;
+                run += (double)e[j];
+                if (pick < 0 && run > target && !pick_last) pick = i + j;
+            }
+        }
+        // the first lane with a pick wins; else the warp's last kept logit
+        const unsigned int has = __ballot_sync(0xffffffffu, pick >= 0);
+        const unsigned int kept = __ballot_sync(0xffffffffu, last_kept >= 0);
+        int result;
+        if (has) result = __shfl_sync(0xffffffffu, pick, __ffs(has) - 1);
+        else if (kept) result = __shfl_sync(0xffffffffu, last_kept, 31 - __clz(kept));
+        else result = 0;
+        if (lane == 0) chosen = result;
     }
+    __syncthreads();
+    if (threadIdx.x == 0) out[row] = chosen < 0 ? 0 : chosen;
 }
 
 // out[row] = log softmax(logits[row])[tokens[row]] = x[token] - max - log(sum exp(x - max)), in
@@ -279,7 +360,7 @@ KL_API int kl_sample_rows(const float* logits, long long row_stride, int rows, i
                           int top_k, unsigned long long seed, const int* request_ids, const int* steps, int* out,
                           cudaStream_t stream) {
     if (rows <= 0) return KL_OK;
-    if (vocab <= 0 || !(temperature > 0.f)) return KL_ERR_BAD_SIZE;
+    if (vocab <= 0 || !(temperature > 0.f) || vocab > SAMPLE_TILE * SAMPLE_MAX_TILES) return KL_ERR_BAD_SIZE;
     launch_kernel(sample_rows_kernel, rows, SAMPLE_THREADS, 0, stream, logits, (size_t)row_stride, vocab, temperature, top_k,
                                                             seed, request_ids, steps, out);
     KL_LAUNCH_CHECK();
