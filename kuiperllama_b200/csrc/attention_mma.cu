@@ -82,7 +82,7 @@ struct DecodeFuse {
 };
 
 template <int HD, int WM, int WN, int NS>
-__global__ void __launch_bounds__(32 * WM * WN, NS == 2 ? 3 : 2)   // NS = 2: three CTAs per SM (168 registers, 3 x 64 KB of stages)
+__global__ void __launch_bounds__(32 * WM * WN, NS == 2 ? ((HD == 64 && WN > 1) ? 4 : 3) : 2)   // NS = 2: three CTAs per SM (168 registers, 3 x 64 KB of stages); four in the decode layout with a head size of 64
 attention_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out,
                      const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                      const int* __restrict__ block_table, int blocks_per_seq,

@@ -39,6 +39,9 @@ HEADERS: List[str] = ["common.cuh", "tcgen05.cuh", "tma_host.cuh", "attention_de
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-shared", "--expt-relaxed-constexpr", "--extended-lambda"]
+# Extra flags for experiments (for instance -DNAME to switch a variant on); they are part of the
+# record that decides whether a built library is current.
+NVCC_FLAGS += os.environ.get("KL_NVCC_FLAGS", "").split()
 
 
 class ExtensionError(RuntimeError):

@@ -6,6 +6,7 @@ missing extension or a refused size raises.
 from __future__ import annotations
 
 import ctypes
+import os
 import threading
 from typing import Dict, Optional
 
@@ -318,6 +319,8 @@ def check_device_words(device: torch.device) -> None:
     if status or bad_id:
         words.zero_()
     if status:
+        for _, flags in _sk_scratch.values():          # a product that gave up may have left its flags set
+            flags.zero_()
         raise KernelError(f"a tensor-core kernel gave up waiting (code {status}: 1 = loader, 2 = MMA issuer, 3 = epilogue); "
                           "the results of this run are not valid")
     if bad_id:
@@ -354,14 +357,33 @@ def sm_count(device: Optional[torch.device] = None) -> int:
     return _sm_counts[idx]
 
 
-def skinny_splits(N: int, K: int) -> int:
+def skinny_splits(N: int, K: int, M: int = 1) -> int:
     """Into how many pieces the K range is cut for a product with few tokens, so that about two
-    CTAs per SM stream weights: 128 output features per CTA, at least 4 k-blocks of 64 each."""
+    CTAs per SM stream weights: 128 output features per CTA, at least 4 k-blocks of 64 each.
+    Every piece is written as float32 [M, N] and read again by the kernel that adds the pieces, so
+    with many tokens and a short k range fewer pieces are better: their bytes stay under a quarter
+    of the weights' (pieces * M * 4 <= K * 2 / 4)."""
     tiles = (N + 127) // 128
     k_blocks = (K + 63) // 64
-    want = max(1, min((2 * sm_count() + tiles // 2) // tiles, k_blocks // 4, 32))
+    want = max(1, min((2 * sm_count() + tiles // 2) // tiles, k_blocks // 4, 32, max(1, K // (8 * max(M, 1)))))
     per = (k_blocks + want - 1) // want
     return (k_blocks + per - 1) // per
+
+
+# The tiles of a product's last, partial round of CTAs are cut along k over all CTAs (see
+# gemm_tcgen05.cu); False (or KL_STREAM_K=0 in the environment) computes every tile whole.
+STREAM_K = os.environ.get("KL_STREAM_K", "1") != "0"
+_sk_scratch: Dict[int, tuple] = {}
+
+
+def _stream_k_scratch(device: torch.device):
+    """Per device, made once: a float32 slot of one 128 x 256 tile and a zero flag for every SM."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx not in _sk_scratch:
+        n = sm_count(device)
+        _sk_scratch[idx] = (torch.empty((n, 128 * 256), dtype=torch.float32, device=device),
+                            torch.zeros(n, dtype=torch.int32, device=device))
+    return _sk_scratch[idx]
 
 
 def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bool = False) -> None:
@@ -373,9 +395,11 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bo
     _need(K == K2 and out.shape[0] >= M and out.shape[1] == (N // 2 if swiglu else N), "gemm_tcgen05: shapes")
     _need(not swiglu or (N % 128 == 0 and out.dtype == torch.bfloat16), "gemm_tcgen05: swiglu needs N % 128 == 0 and bf16 out")
     _need(_tc_ok(a, w, out), "gemm_tcgen05: operands must be bfloat16 with 16-byte aligned rows")
+    partials, flags = _stream_k_scratch(a.device) if STREAM_K else (None, None)
     _check(lib("gemm_tcgen05").kl_gemm_tcgen05(_ptr(a), ctypes.c_longlong(a.stride(0)), _ptr(w),
                                                ctypes.c_longlong(w.stride(0)), _ptr(out), ctypes.c_longlong(out.stride(0)),
                                                M, N, K, int(out.dtype == torch.float32), int(swiglu),
+                                               _ptr(partials), _ptr(flags), 0 if flags is None else flags.numel(),
                                                _ptr(status_word(a.device)), _stream()), "gemm_tcgen05")
 
 
@@ -430,7 +454,7 @@ def gemm_skinny_stream(w: torch.Tensor, a: torch.Tensor, row_scale=None, sink=No
                                         ctypes.c_longlong(out.stride(0)), M, N, K, 1, 0, 1, *scale_args, null, null, null, null,
                                         null, st, _stream()), "gemm_skinny_stream")
         return out
-    splits = skinny_splits(N, K) if splits is None else splits
+    splits = skinny_splits(N, K, M) if splits is None else splits
     partial = torch.empty((splits, M, N), dtype=torch.float32, device=dev)
     result = partial
     sink_args = (null, null, null, null, null)
@@ -464,7 +488,7 @@ def gemm_skinny_partials(a: torch.Tensor, w: torch.Tensor, splits: Optional[int]
     probe = torch.empty((0, N), dtype=torch.float32, device=a.device)
     if not _tc_ok(a, w, probe):
         return None
-    splits = skinny_splits(N, K) if splits is None else splits
+    splits = skinny_splits(N, K, M) if splits is None else splits
     if splits <= 1:
         return None
     partial = torch.empty((splits, M, N), dtype=torch.float32, device=a.device)
@@ -486,7 +510,7 @@ def gemm_skinny(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, splits: Opt
     _need(K == K2 and out.shape[0] >= M and out.shape[1] == (N // 2 if swiglu else N) and M <= 64, "gemm_skinny: shapes")
     _need(_tc_ok(a, w, out), "gemm_skinny: operands must be bfloat16 with 16-byte aligned rows")
     _need(not swiglu or (N % 128 == 0 and out.dtype == torch.bfloat16), "gemm_skinny: swiglu needs N % 128 == 0 and bf16 out")
-    splits = 1 if swiglu else (skinny_splits(N, K) if splits is None else splits)
+    splits = 1 if swiglu else (skinny_splits(N, K, M) if splits is None else splits)
     L = lib("gemm_tcgen05")
     st = _ptr(status_word(a.device))
     if splits == 1:
@@ -652,13 +676,13 @@ def _zero_counters(device: torch.device, n: int, use: str = "attention") -> torc
     return have
 
 
-def decode_attention_splits(n_seqs: int, num_kv_heads: int) -> int:
+def decode_attention_splits(n_seqs: int, num_kv_heads: int, head_dim: int = 128) -> int:
     """Pieces a sequence's keys are cut into for the tensor-core decode kernel: as many as keep
-    all CTAs in one round (three CTAs fit an SM), at most 16.  A CTA's time is its chain of
-    pages, so a second round costs more than longer chains (32 sequences of 8 kv heads: 27 us
-    with one piece, 35 us with two)."""
+    all CTAs in one round (three CTAs fit an SM, four with a head size of 64), at most 16.  A
+    CTA's time is its chain of pages, so a second round costs more than longer chains (32
+    sequences of 8 kv heads: 27 us with one piece, 35 us with two)."""
     ctas = max(1, n_seqs * num_kv_heads)
-    return max(1, min(16, (3 * sm_count()) // ctas))
+    return max(1, min(16, ((4 if head_dim == 64 else 3) * sm_count()) // ctas))
 
 
 def decode_fusable(dtype: torch.dtype, head_dim: int, rotary_dim: int, num_heads: int, num_kv_heads: int) -> bool:
@@ -691,7 +715,7 @@ def attention_decode_fused(qkv: torch.Tensor, inv_freq: torch.Tensor, out: torch
     _need(inv_freq.dtype == torch.float32 and inv_freq.numel() == head_dim // 2, "attention_decode_fused: inv_freq")
     _need(all(t.data_ptr() % 16 == 0 for t in (qkv, inv_freq, out, k_cache, v_cache)), "attention_decode_fused: 16-byte aligned operands")
     if splits is None:
-        splits = decode_attention_splits(n, num_kv_heads)
+        splits = decode_attention_splits(n, num_kv_heads, head_dim)
     po = pml = None
     if splits > 1:
         po = torch.empty((n, num_heads, splits, head_dim), dtype=torch.float32, device=out.device)
@@ -724,7 +748,7 @@ def attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache: torch.
     elif bf and head_dim in MMA_HEAD_DIMS and group <= 16 and (not step.is_decode or DECODE_KERNEL == "mma"):
         splits = 1
         if step.is_decode:
-            splits = decode_attention_splits(step.n_seqs, num_kv_heads)
+            splits = decode_attention_splits(step.n_seqs, num_kv_heads, head_dim)
         attention_mma(q, q_stride, out, k_cache, v_cache, block_table, step.cu_tokens, step.seq_slots, step.seq_starts,
                       step.seq_new, step.n_seqs, step.max_new, step.n_tokens, num_heads, num_kv_heads, head_dim, scale,
                       window, splits, few_rows=step.is_decode)

@@ -112,7 +112,7 @@ def main(argv=None) -> int:
             o = torch.empty(B, H * hd, device=DEV, dtype=torch.bfloat16)
             pos, slots = i32([N - 1] * B), i32(list(range(B)))
             cu, st, nw = i32(list(range(B + 1))), i32([N - 1] * B), i32([1] * B)
-            splits = args.splits or ops.decode_attention_splits(B, KV)
+            splits = args.splits or ops.decode_attention_splits(B, KV, hd)
             if args.fused:
                 from types import SimpleNamespace
                 step = SimpleNamespace(n_seqs=B, n_tokens=B, is_decode=True, cu_tokens=cu, seq_slots=slots, seq_starts=st, seq_new=nw)
