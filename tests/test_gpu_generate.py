@@ -163,6 +163,37 @@ def test_command_line(model_folders):
     assert bad.returncode != 0 and "tokenizer" in bad.stderr
 
 
+def test_command_line_without_a_folder_with_a_prompt_file_logits_and_rates(tmp_path):
+    """``--config FILE --random-weights`` builds the model from a config.json alone; ``--prompt-file`` brings
+    one prompt a line; ``--print-logits`` shows every new token's logit, log-probability and the top five;
+    ``--bench`` runs twice and prints the second run's rates as one JSON line."""
+    import json
+    cfg = tmp_path / "config.json"
+    cfg.write_text(json.dumps(config_dict("tiny2")))
+    prompts = tmp_path / "prompts.txt"
+    prompts.write_text("1, 5, 9\n\n44 45 46 47 48\n")
+    cmd = [sys.executable, os.path.join(ROOT, "bin", "llama_infer"), "--config", str(cfg), "--random-weights", "--seed", "3",
+           "--prompt-file", str(prompts), "--max-new-tokens", "4", "--stop-ids", "", "--print-logits", "--bench", "--max-ctx", "128",
+           "--max-batch", "2"]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    lines = r.stdout.strip().splitlines()
+    tokens = [[int(t) for t in l.split()] for l in lines if l and all(c.isdigit() or c == " " for c in l)]
+    assert [len(t) for t in tokens] == [4, 4]
+    shown = [l for l in lines if l.startswith("  token ")]
+    assert len(shown) == 8
+    first = shown[0].split()                                      # "token T logit X logprob Y | top: i:v ..."
+    assert int(first[1]) == tokens[0][0] and float(first[5]) <= 0.0
+    top = first[first.index("top:") + 1]
+    assert int(top.split(":")[0]) == tokens[0][0] and abs(float(top.split(":")[1]) - float(first[3])) < 1e-3    # greedy: the top one
+    rates = [json.loads(l) for l in lines if l.startswith("{")]
+    assert len(rates) == 1 and rates[0]["prompts"] == 2 and rates[0]["prefill_tokens"] == 8 and rates[0]["decode_steps"] == 3
+    assert rates[0]["decode_tokens_per_s"] > 0
+    # neither a folder nor a configuration: refused with the way out
+    bad = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "llama_infer"), "--random-weights"], capture_output=True, text=True, timeout=600)
+    assert bad.returncode != 0 and "--config" in bad.stderr
+
+
 def test_per_kernel_timing_of_a_generation(model_folders):
     """``profiling.kernel_timing``: every kernel entry point between two CUDA events, summed by name."""
     import kuiperllama_b200 as kl
