@@ -92,6 +92,64 @@ __device__ __forceinline__ void tile_of(int id, int tiles_m, int tiles_n, int& t
 // the products).  For g far below zero the denominator is huge or infinite and the quotient 0, as it should be.
 __device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
 
+// Tokens-as-rows: 32 accumulator columns of one token row to the output (columns n0 .. n0 + 31).
+__device__ __forceinline__ void store_row_chunk(const GemmArgs& args, int row, int n0, const uint32_t (&r)[32]) {
+    const bool full_n = n0 + 32 <= args.rows_b;
+    if (args.out_f32) {
+        float* o = (float*)args.out + (size_t)row * args.ld_out + n0;
+        if (full_n && (args.ld_out & 3) == 0) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4)
+                *reinterpret_cast<uint4*>(o + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+        } else {
+            for (int j = 0; j < 32; ++j)
+                if (n0 + j < args.rows_b) o[j] = __uint_as_float(r[j]);
+        }
+    } else {
+        __nv_bfloat16* o = (__nv_bfloat16*)args.out + (size_t)row * args.ld_out + n0;
+        if (full_n && (args.ld_out & 7) == 0) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+                uint4 v;
+                __nv_bfloat162 p0 = __floats2bfloat162_rn(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
+                __nv_bfloat162 p1 = __floats2bfloat162_rn(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                __nv_bfloat162 p2 = __floats2bfloat162_rn(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]));
+                __nv_bfloat162 p3 = __floats2bfloat162_rn(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
+                v.x = *reinterpret_cast<uint32_t*>(&p0); v.y = *reinterpret_cast<uint32_t*>(&p1);
+                v.z = *reinterpret_cast<uint32_t*>(&p2); v.w = *reinterpret_cast<uint32_t*>(&p3);
+                *reinterpret_cast<uint4*>(o + j) = v;
+            }
+        } else {
+            for (int j = 0; j < 32; ++j)
+                if (n0 + j < args.rows_b) o[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
+        }
+    }
+}
+// The same with the SwiGLU epilogue: 32 gate columns and their 32 up columns give the output features f0 .. f0 + 31.
+__device__ __forceinline__ void store_row_chunk_swiglu(const GemmArgs& args, int row, int f0, const uint32_t (&rg)[32],
+                                                       const uint32_t (&ru)[32]) {
+    const int half_n = args.rows_b / 2;
+    __nv_bfloat16* o = (__nv_bfloat16*)args.out + (size_t)row * args.ld_out + f0;
+    if (f0 + 32 <= half_n && (args.ld_out & 7) == 0) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 8) {
+            uint32_t w[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                __nv_bfloat162 pr = __floats2bfloat162_rn(
+                    silu_mul(__uint_as_float(rg[j + 2 * e]), __uint_as_float(ru[j + 2 * e])),
+                    silu_mul(__uint_as_float(rg[j + 2 * e + 1]), __uint_as_float(ru[j + 2 * e + 1])));
+                w[e] = *reinterpret_cast<uint32_t*>(&pr);
+            }
+            *reinterpret_cast<uint4*>(o + j) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+    } else {
+        for (int j = 0; j < 32; ++j)
+            if (f0 + j < half_n)
+                o[j] = __float2bfloat16_rn(silu_mul(__uint_as_float(rg[j]), __uint_as_float(ru[j])));
+    }
+}
+
 template <int BN, int STAGES, bool WEIGHT_ROWS>
 __global__ void __launch_bounds__(TC_THREADS, WEIGHT_ROWS ? 2 : 1)      // weights-as-rows: two CTAs share an SM
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmArgs args) {
@@ -490,11 +548,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             if (args.swiglu) {
                 // tile columns: 64 gate, 64 up, 64 gate, 64 up -> 128 outputs silu(gate) * up per row
                 uint32_t rg[32], ru[32];
-                const int half_n = args.rows_b / 2;
 #pragma unroll 1
                 for (int c = 0; c < BN / 2; c += 32) {                     // c: output column within the tile
                     const int f0 = tile_b * (BN / 2) + c;
-                    if (f0 >= half_n) break;
+                    if (f0 >= args.rows_b / 2) break;
                     const int col = (c / 64) * 128 + (c % 64);             // gate column in the accumulator
                     if (nkb > 0) { tmem_ld32(taddr + col, rg); tmem_ld32(taddr + col + 64, ru); tmem_ld_wait(); }
                     else {
@@ -502,27 +559,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         for (int j = 0; j < 32; ++j) { rg[j] = 0u; ru[j] = 0u; }
                     }
                     if (sk_n > 0) { add_shares(rg, col); add_shares(ru, col + 64); }
-                    if (row < args.rows_a) {
-                        __nv_bfloat16* o = (__nv_bfloat16*)args.out + (size_t)row * args.ld_out + f0;
-                        if (f0 + 32 <= half_n && (args.ld_out & 7) == 0) {
-#pragma unroll
-                            for (int j = 0; j < 32; j += 8) {
-                                uint32_t w[4];
-#pragma unroll
-                                for (int e = 0; e < 4; ++e) {
-                                    __nv_bfloat162 pr = __floats2bfloat162_rn(
-                                        silu_mul(__uint_as_float(rg[j + 2 * e]), __uint_as_float(ru[j + 2 * e])),
-                                        silu_mul(__uint_as_float(rg[j + 2 * e + 1]), __uint_as_float(ru[j + 2 * e + 1])));
-                                    w[e] = *reinterpret_cast<uint32_t*>(&pr);
-                                }
-                                *reinterpret_cast<uint4*>(o + j) = make_uint4(w[0], w[1], w[2], w[3]);
-                            }
-                        } else {
-                            for (int j = 0; j < 32; ++j)
-                                if (f0 + j < half_n)
-                                    o[j] = __float2bfloat16_rn(silu_mul(__uint_as_float(rg[j]), __uint_as_float(ru[j])));
-                        }
-                    }
+                    if (row < args.rows_a) store_row_chunk_swiglu(args, row, f0, rg, ru);
                 }
             } else {
                 // tile rows are tokens m, tile columns are output features n: out[m][n]
@@ -537,38 +574,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         for (int j = 0; j < 32; ++j) r[j] = 0u;
                     }
                     if (sk_n > 0) add_shares(r, c);
-                    if (row < args.rows_a) {
-                        const bool full_n = n0 + 32 <= args.rows_b;
-                        if (args.out_f32) {
-                            float* o = (float*)args.out + (size_t)row * args.ld_out + n0;
-                            if (full_n && (args.ld_out & 3) == 0) {
-#pragma unroll
-                                for (int j = 0; j < 32; j += 4)
-                                    *reinterpret_cast<uint4*>(o + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
-                            } else {
-                                for (int j = 0; j < 32; ++j)
-                                    if (n0 + j < args.rows_b) o[j] = __uint_as_float(r[j]);
-                            }
-                        } else {
-                            __nv_bfloat16* o = (__nv_bfloat16*)args.out + (size_t)row * args.ld_out + n0;
-                            if (full_n && (args.ld_out & 7) == 0) {
-#pragma unroll
-                                for (int j = 0; j < 32; j += 8) {
-                                    uint4 v;
-                                    __nv_bfloat162 p0 = __floats2bfloat162_rn(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
-                                    __nv_bfloat162 p1 = __floats2bfloat162_rn(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-                                    __nv_bfloat162 p2 = __floats2bfloat162_rn(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]));
-                                    __nv_bfloat162 p3 = __floats2bfloat162_rn(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
-                                    v.x = *reinterpret_cast<uint32_t*>(&p0); v.y = *reinterpret_cast<uint32_t*>(&p1);
-                                    v.z = *reinterpret_cast<uint32_t*>(&p2); v.w = *reinterpret_cast<uint32_t*>(&p3);
-                                    *reinterpret_cast<uint4*>(o + j) = v;
-                                }
-                            } else {
-                                for (int j = 0; j < 32; ++j)
-                                    if (n0 + j < args.rows_b) o[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
-                            }
-                        }
-                    }
+                    if (row < args.rows_a) store_row_chunk(args, row, n0, r);
                 }
             }
         }
@@ -591,6 +597,172 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     tc_fence_before();
     __syncthreads();
     if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, TMEM_COLS); }
+}
+
+// ------------------------------------------------------------------------------------------ pairs of CTAs (prefill)
+// Tokens as rows with tiles of 256 tokens x 256 features worked by two CTAs of a cluster as one
+// (cta_group::2).  Each CTA stages its own 128 token rows and 128 of the tile's 256 weight rows, the
+// CTA of even rank issues MMAs of M = 256, N = 256 that read both CTAs' shared memory and fill both
+// CTAs' tensor memory (each keeps its 128 rows of the result).  Per 64 k a CTA then takes 32 KB of
+// operands from L2 instead of 48 KB for the same products, and that traffic is what bounds the
+// single-CTA kernel above (and costs energy, which bounds the whole prefill step).  TMA loads are
+// plain per-CTA loads that report to the even CTA's barrier; the MMA's completion is committed to
+// both CTAs' barriers.  Persistent: pair p walks the tiles p, p + pairs, ...; two accumulators of 256
+// columns, one drained by both CTAs' epilogue warps while the other is filled.
+template <int STAGES>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmArgs args) {
+    constexpr int BN = 256;
+    constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2, B_BYTES = (BN / 2) * TC_BK * 2;
+    constexpr uint32_t STAGE_TX = 2u * (A_BYTES + B_BYTES);
+    constexpr uint32_t ACC_COLS = BN, TMEM_COLS = 2 * ACC_COLS;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* tiles_a = smem;
+    uint8_t* tiles_b = smem + STAGES * A_BYTES;
+    uint64_t* full = (uint64_t*)(tiles_b + STAGES * B_BYTES);
+    uint64_t* empty = full + STAGES;
+    uint64_t* acc_full = empty + STAGES;
+    uint64_t* acc_empty = acc_full + 2;
+    uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+    const int n_tiles = args.tiles_m * args.tiles_n;              // tiles of 256 x 256
+    const int nkb = args.k_blocks;
+
+    pdl_launch_dependents();
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 8); }   // 4 epilogue warps of each CTA
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0 && lane == 0) { prefetch_tmap(&map_a); prefetch_tmap(&map_b); }
+    if (warp == 1) { tmem_alloc_pair(tmem_slot, TMEM_COLS); tmem_relinquish_pair(); }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync();                                               // the other CTA's barriers exist before anything reports to them
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t rank = cluster_ctarank();
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- TMA producer (both CTAs)
+        if (elect_one()) {
+            int issued = 0;
+            bool ok = true;
+            for (int t = pair; t < n_tiles && ok; t += n_pairs) {
+                int tm, tn;
+                tile_of(t, args.tiles_m, args.tiles_n, tm, tn);
+                const int row_a = tm * 2 * TC_BM + (int)rank * TC_BM, row_b = tn * BN + (int)rank * (BN / 2);
+                int first = 0;
+                if (issued == 0) {
+                    // weights before this grid waits for the kernel ahead, activations after
+                    const int pre = min(nkb, STAGES);
+                    for (int i = 0; i < pre; ++i) {
+                        if (rank == 0) mbar_expect_tx(&full[i], STAGE_TX);
+                        tma_load_2d_pair(tiles_b + i * B_BYTES, &map_b, mapa(smem_u32(&full[i]), 0), i * TC_BK, row_b);
+                    }
+                    pdl_wait();
+                    for (int i = 0; i < pre; ++i)
+                        tma_load_2d_pair(tiles_a + i * A_BYTES, &map_a, mapa(smem_u32(&full[i]), 0), i * TC_BK, row_a);
+                    issued = first = pre;
+                }
+                for (int i = first; i < nkb; ++i) {
+                    const int s = issued % STAGES;
+                    if (issued >= STAGES && !mbar_wait(&empty[s], ((issued / STAGES) - 1) & 1, abort_flag, args.status, 1)) { ok = false; break; }
+                    if (rank == 0) mbar_expect_tx(&full[s], STAGE_TX);
+                    const uint32_t bar = mapa(smem_u32(&full[s]), 0);
+                    tma_load_2d_pair(tiles_a + s * A_BYTES, &map_a, bar, i * TC_BK, row_a);
+                    tma_load_2d_pair(tiles_b + s * B_BYTES, &map_b, bar, i * TC_BK, row_b);
+                    ++issued;
+                }
+            }
+            if (issued == 0) pdl_wait();
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------- MMA issuer (the even CTA, for both)
+        if (rank == 0 && elect_one()) {
+            constexpr uint32_t idesc = umma_idesc(BN, 2 * TC_BM);
+            pdl_wait();
+            bool ok = true;
+            int it = 0, lt = 0;
+            for (int t = pair; t < n_tiles && ok; t += n_pairs, ++lt) {
+                const int buf = lt & 1, use = lt >> 1;
+                if (use > 0) {                                // both CTAs' epilogues must have read this accumulator out
+                    ok = mbar_wait(&acc_empty[buf], (use - 1) & 1, abort_flag, args.status, 4);
+                    if (!ok) break;
+                    tc_fence_after();
+                }
+                const uint32_t tmem_acc = tmem_base + buf * ACC_COLS;
+                for (int i = 0; i < nkb; ++i, ++it) {
+                    const int s = it % STAGES;
+                    ok = mbar_wait(&full[s], (it / STAGES) & 1, abort_flag, args.status, 2);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint64_t da = smem_desc_sw128(smem_u32(tiles_a + s * A_BYTES));
+                    const uint64_t db = smem_desc_sw128(smem_u32(tiles_b + s * B_BYTES));
+#pragma unroll
+                    for (int k = 0; k < TC_BK / 16; ++k)
+                        umma_bf16_pair(tmem_acc, da + 2 * k, db + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+                    umma_commit_pair(&empty[s], 3);           // the stage is free in both CTAs once these MMAs have read it
+                }
+                if (!ok) break;
+                umma_commit_pair(&acc_full[buf], 3);
+            }
+        }
+    } else {
+        // ---------------------------------------------------------------- epilogue: warps 2..5 of both CTAs, 128 rows each
+        const int quarter = warp & 3;
+        pdl_wait();
+        int lt = 0;
+        for (int t = pair; t < n_tiles; t += n_pairs, ++lt) {
+            int tm, tn;
+            tile_of(t, args.tiles_m, args.tiles_n, tm, tn);
+            const int buf = lt & 1;
+            const bool ok = mbar_wait(&acc_full[buf], (lt >> 1) & 1, abort_flag, args.status, 3) && !*abort_flag;
+            tc_fence_after();
+            const int row = tm * 2 * TC_BM + (int)rank * TC_BM + quarter * 32 + lane;
+            const uint32_t taddr = tmem_base + buf * ACC_COLS + ((uint32_t)(quarter * 32) << 16);
+            if (ok && args.swiglu) {
+                uint32_t rg[32], ru[32];
+#pragma unroll 1
+                for (int c = 0; c < BN / 2; c += 32) {
+                    const int f0 = tn * (BN / 2) + c;
+                    if (f0 >= args.rows_b / 2) break;
+                    const int col = (c / 64) * 128 + (c % 64);
+                    if (nkb > 0) { tmem_ld32(taddr + col, rg); tmem_ld32(taddr + col + 64, ru); tmem_ld_wait(); }
+                    else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) { rg[j] = 0u; ru[j] = 0u; }
+                    }
+                    if (row < args.rows_a) store_row_chunk_swiglu(args, row, f0, rg, ru);
+                }
+            } else if (ok) {
+                uint32_t r[32];
+#pragma unroll 1
+                for (int c = 0; c < BN; c += 32) {
+                    const int n0 = tn * BN + c;
+                    if (n0 >= args.rows_b) break;
+                    if (nkb > 0) { tmem_ld32(taddr + c, r); tmem_ld_wait(); }
+                    else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) r[j] = 0u;
+                    }
+                    if (row < args.rows_a) store_row_chunk(args, row, n0, r);
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(mapa(smem_u32(&acc_empty[buf]), 0));
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync();                 // neither CTA leaves (or frees tensor memory) while the other may still reach into it
+    if (warp == 1) { tc_fence_after(); tmem_dealloc_pair(tmem_base, TMEM_COLS); }
 }
 
 // ------------------------------------------------------------------------------------------ host side
@@ -617,6 +789,29 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& 
     return KL_OK;
 }
 
+// KL_GEMM_PAIRS=0 in the environment keeps every CTA on its own (for comparisons).
+static bool pairs_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("KL_GEMM_PAIRS");
+        v = (e != nullptr && e[0] == '0') ? 0 : 1;
+    }
+    return v != 0;
+}
+
+static int launch_pairs(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& args, int grid_x, cudaStream_t stream) {
+    constexpr int STAGES = 6;
+    constexpr size_t smem = (size_t)STAGES * (TC_BM * TC_BK * 2 + 128 * TC_BK * 2) + (2 * STAGES + 4) * 8 + 16 + 1024;
+    static bool configured = false;
+    if (!configured) {
+        KL_CUDA(cudaFuncSetAttribute(gemm_pair_kernel<STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured = true;
+    }
+    launch_kernel_clustered(gemm_pair_kernel<STAGES>, 2, dim3(grid_x, 1, 1), TC_THREADS, smem, stream, ma, mb, args);
+    KL_LAUNCH_CHECK();
+    return KL_OK;
+}
+
 static bool aligned_operand(const void* p, long long ld, int K) {
     return ((uintptr_t)p & 15) == 0 && (ld % 8) == 0 && (K % 8) == 0 && K > 0;
 }
@@ -639,6 +834,17 @@ KL_API int kl_gemm_tcgen05(const void* a, long long lda, const void* w, long lon
     CUtensorMap ma, mb;
     int rc;
     if ((rc = make_map(&ma, a, M, K, lda, TC_BM)) != KL_OK) return rc;
+    // Pairs of CTAs on tiles of 256 tokens where that wastes no rows to speak of: an even number of
+    // 128-token tiles, or so many tokens that half a tile of padding is little.
+    if (pairs_enabled() && (((M + TC_BM - 1) / TC_BM) % 2 == 0 || M >= 1024)) {
+        const int sms2 = kl::sm_count();
+        if (sms2 <= 1) return KL_ERR_SETUP;
+        if ((rc = make_map(&mb, w, N, K, ldw, 128)) != KL_OK) return rc;
+        const int tiles_m2 = (M + 2 * TC_BM - 1) / (2 * TC_BM), tiles_n2 = (N + 255) / 256;
+        if ((long long)tiles_m2 * tiles_n2 > 0x3fffffffLL) return KL_ERR_BAD_SIZE;
+        GemmArgs pargs{out, ldo, 0, M, N, (K + TC_BK - 1) / TC_BK, out_f32, status, tiles_m2, tiles_n2, swiglu};
+        return launch_pairs(ma, mb, pargs, 2 * min(tiles_m2 * tiles_n2, sms2 / 2), stream);
+    }
     if ((rc = make_map(&mb, w, N, K, ldw, 256)) != KL_OK) return rc;
     const int tiles_m = (M + TC_BM - 1) / TC_BM, tiles_n = (N + 255) / 256;
     GemmArgs args{out, ldo, 0, M, N, (K + TC_BK - 1) / TC_BK, out_f32, status, tiles_m, tiles_n, swiglu};
