@@ -8,9 +8,10 @@
 // and issues the MMAs, warps 2..5 are the epilogue (their index mod 4 picks the quarter of
 // the 128 tensor-memory lanes that each may read).
 //
-// Two ways of laying a product on the 128 x BN tile:
-//   * tokens as rows (prefill): A = activations [M, K], B = weights [N, K], tile 128 x 256;
-//     out[m, n] in bfloat16 or float32.
+// Ways of laying a product on tiles:
+//   * tokens as rows (prefill): A = activations [M, K], B = weights [N, K]; out[m, n] in bfloat16
+//     or float32.  Tiles of 256 x 256 worked by pairs of CTAs as one (gemm_pair_kernel, cta_group::2)
+//     where the token count suits, else tiles of 128 x 256 by single CTAs.
 //   * weights as rows (decode, few tokens): A = weights [N, K], B = activations [M <= 64, K],
 //     tile 128 x {16, 32, 64}; the K range may be cut over blockIdx.z, each cut writing
 //     float32 partial sums [z, M, N] that the caller's reduction adds in a fixed order.  Every
@@ -57,21 +58,6 @@ struct GemmArgs {
     int* sink_counters;       //   128 columns per row in sink_ss[tile][64]; counters are zero between launches
     const float* sink_w;      // with sink: the next norm's weight [rows_a], and where bf16(x * w) of the new
     __nv_bfloat16* sink_scaled;   //   rows goes [rows_b, rows_a] (the next product's activations); may be null
-    // Tokens-as-rows only: the last sk_tiles tiles (those that would not fill a round of CTAs) are cut
-    // along k into sk_ctas equal shares, one for each of the first sk_ctas CTAs (see "the partial round").
-    int sk_tiles;
-    int sk_ctas;
-    float* sk_partials;       // [sk_ctas][8 x 128 x 32] float32: a CTA's share of a tile it does not finish
-    int* sk_flags;            // [sk_ctas], zero between launches: 1 = that CTA's share is in sk_partials
-};
-
-// One stretch of work of a CTA: the k blocks [kb0, kb1) of one tile.
-struct WorkItem {
-    int tile_a, tile_b;       // tile row (A operand) and tile column (B operand)
-    int kb0, kb1;
-    int kind;                 // 0: the whole k range; 1: a share whose sums go to sk_partials[this CTA];
-                              // 2: the share that ends the tile: adds the shares of the CTAs [first_cta, this CTA) and writes
-    int first_cta;
 };
 
 // Tile order for tokens-as-rows: all the feature tiles of a group of TC_GROUP_M token tiles
@@ -168,61 +154,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // The CTA's work, item by item; the three roles below walk the same list.
-    //   weights-as-rows: one item, the tile blockIdx.x over the k range of blockIdx.z;
-    //   tokens-as-rows: this CTA's share of the last sk_tiles tiles, then, whole, the tiles
-    //   blockIdx.x, blockIdx.x + gridDim.x, ... among the first dp_tiles.
-    // The partial round.  When the tiles do not fill a last round of CTAs, the tiles of that round
-    // are not handed out whole (most SMs would idle through a tile's time): their k blocks, laid
-    // end to end, are cut into sk_ctas equal shares.  A share covers at most two tiles (there are
-    // no more such tiles than shares): the end of one and the start of the next.  The share that
-    // ends a tile owns it: it waits for the earlier shares of that tile, which their CTAs left as
-    // float32 in sk_partials, adds them in ascending k and writes the output.  Every CTA works on
-    // the share it does not own first, so an owner never waits for work that waits for it; and the
-    // shares come before the whole tiles, so that an owner's longer epilogue runs under the next
-    // tile's products.
-    const int n_all = WEIGHT_ROWS ? 0 : args.tiles_m * args.tiles_n;
-    const int dp_tiles = n_all - (WEIGHT_ROWS ? 0 : args.sk_tiles);
-    const int n_dp = WEIGHT_ROWS ? 1 : ((int)blockIdx.x < dp_tiles ? (dp_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0);
-    const bool sk_mine = !WEIGHT_ROWS && (int)blockIdx.x < args.sk_ctas;
-    const long long sk_units = sk_mine ? (long long)args.sk_tiles * args.k_blocks : 0;
-    const long long sk_u0 = sk_mine ? sk_units * blockIdx.x / args.sk_ctas : 0;
-    const long long sk_u1 = sk_mine ? sk_units * (blockIdx.x + 1) / args.sk_ctas : 0;
-    const int sk_first_tile = sk_u1 > sk_u0 ? (int)(sk_u0 / args.k_blocks) : 0;
-    // the share crosses into a second tile?
-    const bool sk_two = sk_u1 > sk_u0 && (sk_u1 - 1) / args.k_blocks != sk_first_tile;
-    const int n_sk = sk_u1 > sk_u0 ? (sk_two ? 2 : 1) : 0;
-    const int n_items = n_dp + n_sk;
-    auto item_at = [&](int idx, WorkItem& w) {
-        w.kind = 0;
-        w.first_cta = 0;
-        if constexpr (WEIGHT_ROWS) {
-            const int per = (args.k_blocks + gridDim.z - 1) / gridDim.z;
-            w.tile_a = blockIdx.x; w.tile_b = 0;
-            w.kb0 = min(args.k_blocks, (int)blockIdx.z * per);
-            w.kb1 = min(args.k_blocks, w.kb0 + per);
-            return;
-        } else {
-            if (idx >= n_sk) {
-                tile_of((int)blockIdx.x + (idx - n_sk) * (int)gridDim.x, args.tiles_m, args.tiles_n, w.tile_a, w.tile_b);
-                w.kb0 = 0; w.kb1 = args.k_blocks;
-                return;
-            }
-            // the second tile's start (a share that never ends its tile) comes first, then the first tile's part
-            const bool second = sk_two && idx == 0;
-            const int t = sk_first_tile + (second ? 1 : 0);
-            const long long t0 = (long long)t * args.k_blocks;
-            w.kb0 = second ? 0 : (int)(sk_u0 - t0);
-            w.kb1 = (int)(min(sk_u1, t0 + args.k_blocks) - t0);
-            tile_of(dp_tiles + t, args.tiles_m, args.tiles_n, w.tile_a, w.tile_b);
-            if (w.kb1 < args.k_blocks) { w.kind = 1; return; }
-            if (w.kb0 == 0) return;                               // the whole tile after all
-            w.kind = 2;
-            int c = blockIdx.x;                                   // the CTAs before this one whose shares reach into the tile
-            while (c > 0 && sk_units * c / args.sk_ctas > t0) --c;
-            w.first_cta = c;
-        }
+    // A CTA takes the tiles blockIdx.x, blockIdx.x + gridDim.x, ... (tokens-as-rows: one CTA per
+    // SM walks many tiles; weights-as-rows: the grid has one CTA per tile).
+    const int n_tiles = WEIGHT_ROWS ? (int)gridDim.x : args.tiles_m * args.tiles_n;
+    auto tile_at = [&](int t, int& ta, int& tb) {
+        if constexpr (WEIGHT_ROWS) { ta = t; tb = 0; }
+        else tile_of(t, args.tiles_m, args.tiles_n, ta, tb);
     };
+    // k range of this CTA (cut over blockIdx.z)
+    const int per = (args.k_blocks + gridDim.z - 1) / gridDim.z;
+    const int kb0 = blockIdx.z * per;
+    const int kb1 = min(args.k_blocks, kb0 + per);
+    const int nkb = max(kb1 - kb0, 0);
 
     pdl_launch_dependents();                    // the next kernel in the stream may set itself up while this one runs
     if (threadIdx.x == 0) {
@@ -243,10 +186,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         if (elect_one()) {
             int issued = 0;                                   // k blocks requested so far, over all tiles
             bool ok = true;
-            for (int idx = 0; idx < n_items && ok; ++idx) {
-                WorkItem w;
-                item_at(idx, w);
-                const int tile_a = w.tile_a, tile_b = w.tile_b, kb0 = w.kb0, nkb = w.kb1 - w.kb0;
+            for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+                int tile_a, tile_b;
+                tile_at(t, tile_a, tile_b);
                 int first = 0;
                 if (issued == 0) {
                     // Weights are written by no kernel, so their tiles for the first stages are requested
@@ -289,11 +231,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             // count this kernel's own progress only.
             pdl_wait();
             bool ok = true;
-            int it = 0;                                       // k blocks consumed, over all items
-            for (int lt = 0; lt < n_items && ok; ++lt) {
-                WorkItem w;
-                item_at(lt, w);
-                const int nkb = w.kb1 - w.kb0;
+            int it = 0, lt = 0;                               // k blocks consumed, tiles done (both over all tiles)
+            for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++lt) {
                 const int buf = lt & 1, use = lt >> 1;
                 if (use > 0) {                                // the epilogue must have read this accumulator out
                     ok = mbar_wait(&acc_empty[buf], (use - 1) & 1, abort_flag, args.status, 4);
@@ -336,88 +275,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             }
             asm volatile("bar.sync 1, 128;" ::: "memory");
         }
-        for (int lt = 0; lt < n_items; ++lt) {
-        WorkItem w;
-        item_at(lt, w);
-        const int tile_a = w.tile_a, tile_b = w.tile_b, nkb = w.kb1 - w.kb0;
+        int lt = 0;
+        for (int t = blockIdx.x; t < n_tiles; t += gridDim.x, ++lt) {
+        int tile_a, tile_b;
+        tile_at(t, tile_a, tile_b);
         const int buf = lt & 1;
-        bool ok = mbar_wait(&acc_full[buf], (lt >> 1) & 1, abort_flag, args.status, 3) && !*abort_flag;
+        const bool ok = mbar_wait(&acc_full[buf], (lt >> 1) & 1, abort_flag, args.status, 3) && !*abort_flag;
         tc_fence_after();
         const int row = tile_a * TC_BM + quarter * 32 + lane;              // row of the A operand
         const uint32_t taddr = tmem_base + buf * ACC_COLS + ((uint32_t)(quarter * 32) << 16);
-        // Shares of a tile of the last round (tokens-as-rows).  A share that does not end its tile leaves
-        // its sums in this CTA's slot of sk_partials; the share that ends the tile adds the slots of
-        // the CTAs before it (ascending k) to its own sums before it writes.
-        const float* sk_add = nullptr;                                     // slot of the first earlier share, this thread's row
-        int sk_n = 0;
-        if constexpr (!WEIGHT_ROWS) {
-            constexpr size_t SLOT = (size_t)TC_BM * BN;
-            if (w.kind == 1) {
-                if (ok) {
-                    // a slot is laid out [chunk of 32 columns][row][32]: a warp writes (and an owner reads) 4 KB runs
-                    float* mine = args.sk_partials + (size_t)blockIdx.x * SLOT + (size_t)(quarter * 32 + lane) * 32;
-                    uint32_t r[32];
-#pragma unroll 1
-                    for (int c = 0; c < BN; c += 32) {
-                        if (nkb > 0) { tmem_ld32(taddr + c, r); tmem_ld_wait(); }
-                        else {
-#pragma unroll
-                            for (int j = 0; j < 32; ++j) r[j] = 0u;
-                        }
-#pragma unroll
-                        for (int j = 0; j < 32; j += 4)
-                            *reinterpret_cast<uint4*>(mine + (size_t)(c / 32) * (TC_BM * 32) + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
-                    }
-                    __threadfence();
-                }
-                asm volatile("bar.sync 1, 128;" ::: "memory");             // all four warps have written and fenced
-                if (ok && threadIdx.x == 64)
-                    asm volatile("st.release.gpu.global.b32 [%0], %1;" ::"l"(args.sk_flags + blockIdx.x), "r"(1) : "memory");
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&acc_empty[buf]);
-                continue;
-            }
-            if (w.kind == 2) {
-                sk_n = (int)blockIdx.x - w.first_cta;
-                sk_add = args.sk_partials + (size_t)w.first_cta * SLOT + (size_t)(quarter * 32 + lane) * 32;
-                // every earlier share must have landed; one lane per warp watches the flags
-                if (ok && lane == 0) {
-                    for (int c = w.first_cta; c < (int)blockIdx.x && ok; ++c) {
-                        uint32_t seen = 0, polls = 0;
-                        while (true) {
-                            asm volatile("ld.acquire.gpu.global.b32 %0, [%1];" : "=r"(seen) : "l"(args.sk_flags + c) : "memory");
-                            if (seen != 0u) break;
-                            if (++polls >= SPIN_LIMIT || ((polls & 1023u) == 0u && *abort_flag)) { ok = false; break; }
-                        }
-                    }
-                    if (!ok) { *abort_flag = 1; atomicCAS(args.status, 0, 5); }
-                }
-                ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-                if (!ok) sk_n = 0;
-            }
-        }
-        auto add_shares = [&](uint32_t (&r)[32], int col) {                // r += the earlier shares' columns col .. col + 31
-            constexpr size_t SLOT = (size_t)TC_BM * BN;
-            // Two shares' loads are requested together (an owner rarely has more): the reads come from L2
-            // while the loader streams operands through it, and what counts is the number of round trips.
-            const float* from = sk_add + (size_t)(col / 32) * (TC_BM * 32);
-            for (int p = 0; p < sk_n; p += 2, from += 2 * SLOT) {
-                const bool two = p + 1 < sk_n;
-                float4 a[8], b[8];
-#pragma unroll
-                for (int j = 0; j < 8; ++j) a[j] = __ldcg(reinterpret_cast<const float4*>(from) + j);
-#pragma unroll
-                for (int j = 0; j < 8; ++j) b[j] = two ? __ldcg(reinterpret_cast<const float4*>(from + SLOT) + j) : make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {                              // ascending k: the earlier share first
-                    r[4 * j] = __float_as_uint((__uint_as_float(r[4 * j]) + a[j].x) + b[j].x);
-                    r[4 * j + 1] = __float_as_uint((__uint_as_float(r[4 * j + 1]) + a[j].y) + b[j].y);
-                    r[4 * j + 2] = __float_as_uint((__uint_as_float(r[4 * j + 2]) + a[j].z) + b[j].z);
-                    r[4 * j + 3] = __float_as_uint((__uint_as_float(r[4 * j + 3]) + a[j].w) + b[j].w);
-                }
-            }
-        };
         if constexpr (WEIGHT_ROWS) {
             if (args.swiglu) {
                 // Tile rows 0..63 are gate features, 64..127 the up rows of the same features.  The
@@ -558,7 +424,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
                         for (int j = 0; j < 32; ++j) { rg[j] = 0u; ru[j] = 0u; }
                     }
-                    if (sk_n > 0) { add_shares(rg, col); add_shares(ru, col + 64); }
                     if (row < args.rows_a) store_row_chunk_swiglu(args, row, f0, rg, ru);
                 }
             } else {
@@ -573,25 +438,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
                         for (int j = 0; j < 32; ++j) r[j] = 0u;
                     }
-                    if (sk_n > 0) add_shares(r, c);
                     if (row < args.rows_a) store_row_chunk(args, row, n0, r);
                 }
-            }
-        }
-        if constexpr (!WEIGHT_ROWS) {
-            if (w.kind == 2) {
-                // the earlier shares are read: their flags go back to zero for the next launch
-                asm volatile("bar.sync 1, 128;" ::: "memory");
-                if (threadIdx.x == 64)
-                    for (int c = w.first_cta; c < (int)blockIdx.x; ++c) args.sk_flags[c] = 0;
             }
         }
         // this accumulator may be filled again once all four warps have read it out
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&acc_empty[buf]);
-        // A warp that gave up walks the rest of the list all the same (its waits return at once and it
-        // writes nothing): the four warps meet at named barriers further down the list.
+        if (!ok) break;
         }
     }
     tc_fence_before();
@@ -822,12 +677,8 @@ using namespace kl;
 
 // out[M, N] = a[M, K] * w[N, K]^T, tokens as tile rows (any M).  out is bf16 (out_f32 = 0) or
 // float32.  Needs 16-byte aligned bases and row strides (K % 8 == 0): else KL_ERR_BAD_ALIGN.
-// sk_partials (float32 [sk_slots][128 * 256]) and sk_flags (int32 [sk_slots], zero, left zero) are scratch
-// for the last round's tiles (see the kernel); with null pointers, or fewer slots than the device has
-// SMs, every tile is computed whole by one CTA.
 KL_API int kl_gemm_tcgen05(const void* a, long long lda, const void* w, long long ldw, void* out, long long ldo, int M,
-                           int N, int K, int out_f32, int swiglu, float* sk_partials, int* sk_flags, int sk_slots,
-                           int* status, cudaStream_t stream) {
+                           int N, int K, int out_f32, int swiglu, int* status, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return KL_OK;
     if (swiglu && (out_f32 || N % 128)) return KL_ERR_BAD_SIZE;
     if (!aligned_operand(a, lda, K) || !aligned_operand(w, ldw, K)) return KL_ERR_BAD_ALIGN;
@@ -852,24 +703,7 @@ KL_API int kl_gemm_tcgen05(const void* a, long long lda, const void* w, long lon
     const int sms = kl::sm_count();
     if (sms <= 0) return KL_ERR_SETUP;
     const int tiles = tiles_m * tiles_n;
-    int grid_x = min(tiles, sms);                     // one CTA per SM walks the tiles
-    // The tiles of a last, partial round are cut along k over the CTAs when that pays: the round
-    // then takes its share of a tile's time instead of a whole one.  An owner's epilogue reads the
-    // other shares' sums through an L2 that the loaders keep busy, which takes about as long as 64 k
-    // blocks of products; so shares pay only under a whole tile of a long k range that follows them
-    // (measured at 2,048 tokens: 4096 x 14336 162 us against 180 us, 4096 x 4096 68 us against 62 us).
-    // At most three shares per tile.  Needs the caller's scratch.
-    if (sk_partials != nullptr && sk_flags != nullptr && sk_slots >= sms) {
-        const int left = tiles % sms;
-        const int ctas = min(sms, 3 * left);
-        if (left > 0 && tiles > sms && left * 8 <= sms * 7 && args.k_blocks >= 128) {
-            grid_x = max(grid_x, ctas);
-            args.sk_tiles = left;
-            args.sk_ctas = ctas;
-            args.sk_partials = sk_partials;
-            args.sk_flags = sk_flags;
-        }
-    }
+    const int grid_x = min(tiles, sms);               // one CTA per SM walks the tiles
     dim3 grid(grid_x, 1, 1);
     return launch<256, 4, false>(ma, mb, args, grid, stream);
 }

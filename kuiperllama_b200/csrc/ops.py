@@ -319,8 +319,6 @@ def check_device_words(device: torch.device) -> None:
     if status or bad_id:
         words.zero_()
     if status:
-        for _, flags in _sk_scratch.values():          # a product that gave up may have left its flags set
-            flags.zero_()
         raise KernelError(f"a tensor-core kernel gave up waiting (code {status}: 1 = loader, 2 = MMA issuer, 3 = epilogue); "
                           "the results of this run are not valid")
     if bad_id:
@@ -370,24 +368,9 @@ def skinny_splits(N: int, K: int, M: int = 1) -> int:
     return (k_blocks + per - 1) // per
 
 
-# The tiles of a product's last, partial round of CTAs are cut along k over all CTAs (see
-# gemm_tcgen05.cu); False (or KL_STREAM_K=0 in the environment) computes every tile whole.
-STREAM_K = os.environ.get("KL_STREAM_K", "1") != "0"
-_sk_scratch: Dict[int, tuple] = {}
-
-
-def _stream_k_scratch(device: torch.device):
-    """Per device, made once: a float32 slot of one 128 x 256 tile and a zero flag for every SM."""
-    idx = device.index if device.index is not None else torch.cuda.current_device()
-    if idx not in _sk_scratch:
-        n = sm_count(device)
-        _sk_scratch[idx] = (torch.empty((n, 128 * 256), dtype=torch.float32, device=device),
-                            torch.zeros(n, dtype=torch.int32, device=device))
-    return _sk_scratch[idx]
-
-
 def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bool = False) -> None:
-    """out[M, N] = a @ w^T on the tensor cores, tokens as tile rows (any M).  With ``swiglu``
+    """out[M, N] = a @ w^T on the tensor cores, tokens as tile rows (any M; pairs of CTAs on tiles of
+    256 tokens where the token count suits, single CTAs on tiles of 128 otherwise).  With ``swiglu``
     the rows of ``w`` alternate 64 gate rows and 64 up rows and out[M, N / 2] receives
     silu(gate) * up."""
     _cuda(a, w, out)
@@ -395,11 +378,9 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bo
     _need(K == K2 and out.shape[0] >= M and out.shape[1] == (N // 2 if swiglu else N), "gemm_tcgen05: shapes")
     _need(not swiglu or (N % 128 == 0 and out.dtype == torch.bfloat16), "gemm_tcgen05: swiglu needs N % 128 == 0 and bf16 out")
     _need(_tc_ok(a, w, out), "gemm_tcgen05: operands must be bfloat16 with 16-byte aligned rows")
-    partials, flags = _stream_k_scratch(a.device) if STREAM_K else (None, None)
     _check(lib("gemm_tcgen05").kl_gemm_tcgen05(_ptr(a), ctypes.c_longlong(a.stride(0)), _ptr(w),
                                                ctypes.c_longlong(w.stride(0)), _ptr(out), ctypes.c_longlong(out.stride(0)),
                                                M, N, K, int(out.dtype == torch.float32), int(swiglu),
-                                               _ptr(partials), _ptr(flags), 0 if flags is None else flags.numel(),
                                                _ptr(status_word(a.device)), _stream()), "gemm_tcgen05")
 
 

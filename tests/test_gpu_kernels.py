@@ -349,20 +349,19 @@ def test_sample_rows_is_the_inverse_cdf_of_the_counter_draw(ops, vocab, temperat
 # ----------------------------------------------------------------------------- tensor-core products
 
 @pytest.mark.parametrize("out_dtype", ["bfloat16", "float32"])
-# The last two shapes have a long k range and a last round of tiles that does not fill the SMs: those
-# tiles are cut along k over the CTAs (256 tiles: one whole round and 108 tiles shared; 320 tiles with
-# ragged edges in both directions: two rounds and 24 tiles shared).
+# Shapes with an even number of 128-token tiles (or 1,024 tokens and more) run on pairs of CTAs with tiles
+# of 256 x 256, the others on single CTAs with tiles of 128 x 256; ragged edges in both directions for both.
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (65, 72, 136), (300, 1000, 520), (2048, 512, 4096), (129, 257, 72),
-                                   (1000, 130, 1024), (2048, 4096, 512), (2048, 4096, 8192), (2000, 5000, 8200)])
-def test_gemm_tcgen05(ops, out_dtype, M, N, K, monkeypatch):
+                                   (1000, 130, 1024), (2048, 4096, 512), (2000, 5000, 2056), (700, 4096, 1024), (1100, 300, 264),
+                                   (640, 4096, 8192)])
+def test_gemm_tcgen05(ops, out_dtype, M, N, K):
     torch.manual_seed(10)
     a = torch.randn(M, K, device=DEV).bfloat16()
     w = torch.randn(N, K, device=DEV).bfloat16()
     ref = a.double().cpu() @ w.double().cpu().T
     tol = {"float32": 2.0 * 2.0 ** -24 * math.sqrt(K), "bfloat16": 8e-3}[out_dtype]
     outs = []
-    for shared_last_round in (True, True, False):                  # twice in a row: the scratch flags are left clean
-        monkeypatch.setattr(ops, "STREAM_K", shared_last_round)
+    for _ in range(2):
         out = torch.full((M, N), 7.0, device=DEV, dtype=DT[out_dtype])
         ops.gemm_tcgen05(a, w, out)
         ops.check_status(out.device)
@@ -370,8 +369,6 @@ def test_gemm_tcgen05(ops, out_dtype, M, N, K, monkeypatch):
         assert err <= tol * float(ref.abs().max()), f"tcgen05 gemm {M}x{N}x{K} -> {out_dtype}: error {err:.3e}"
         outs.append(out)
     assert torch.equal(outs[0], outs[1])
-    partials, flags = ops._stream_k_scratch(torch.device(DEV))
-    assert int(flags.abs().sum()) == 0
 
 
 @pytest.mark.parametrize("out_dtype", ["bfloat16", "float32"])
@@ -601,7 +598,7 @@ def test_the_windows_edge_is_exact(ops, kernel, window, n):
 
 
 @pytest.mark.parametrize("M,I,K", [(1, 64, 64), (8, 512, 192), (33, 14336 // 8, 4096 // 8), (64, 128, 72), (65, 512, 192),
-                                   (300, 1792, 520), (2048, 256, 4096), (2048, 2560, 8192)])
+                                   (300, 1792, 520), (2048, 256, 4096), (2048, 2560, 2048), (1100, 1792, 520)])
 def test_gate_up_product_with_swiglu_epilogue(ops, M, I, K):
     torch.manual_seed(18)
     x = torch.randn(M, K, device=DEV).bfloat16()
