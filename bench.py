@@ -43,7 +43,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 _LLAMA3_ROPE = {"rope_type": "llama3", "low_freq_factor": 1.0, "high_freq_factor": 4.0, "original_max_position_embeddings": 8192}
-# The layer sizes of BASELINE.json's third, fourth and fifth configurations.
+# The layer sizes of the three workloads: Llama-3.1-8B, Llama-2-7B and Llama-3.2-1B.
 LLAMA31_8B = {
     "architectures": ["LlamaForCausalLM"], "hidden_size": 4096, "intermediate_size": 14336,
     "num_hidden_layers": 32, "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128,
