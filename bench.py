@@ -187,10 +187,10 @@ def verify_graph_replay(eng, slots, tokens):
     difference between the two steps' logits (0 expected: the same kernels on the same data)."""
     import torch
     n = len(slots)
-    assert n not in eng._graphs, "the graph of this batch size exists already"
+    assert n not in eng.graph_sizes(), "the graph of this batch size exists already"
     before = [eng.cache.lengths[s] for s in slots]
     eager = eng.decode_step(slots, tokens).clone()
-    assert n in eng._graphs
+    assert n in eng.graph_sizes()
     for s, b in zip(slots, before):
         eng.cache.lengths[s] = b
     replayed = eng.decode_step(slots, tokens)
@@ -229,7 +229,7 @@ def time_decode(infer, batch, steps, warmup, seed, checks):
         slots = [eng.alloc_slot() for _ in range(batch)]
         logits = eng.step([SequenceInput(s, p, [len(p) - 1]) for s, p in zip(slots, prompts)])
         tokens = _Tokens(sampler.sample(logits, empty, empty))
-        if eng.use_graphs and batch not in eng._graphs:
+        if eng.use_graphs and batch not in eng.graph_sizes():
             diff = verify_graph_replay(eng, slots, tokens.read())
             checks[f"graph_replay_b{batch}_max_logit_diff"] = diff
         for _ in range(warmup):
@@ -308,7 +308,8 @@ def run_workload(kl, cfg, name, n_seqs, lo, hi, new_tokens, temperature, pk, see
            "decode_steps": new_tokens - 1, "temperature": temperature}
     for graphs in (True, False):
         infer = kl.Inference(model, max_tokens=held, max_batch=n_seqs, max_seq_len=hi + new_tokens, use_graphs=graphs)
-        infer.generate(prompts, max_new_tokens=3, temperature=temperature, seed=1, stop_ids=[])      # warm-up; captures the graph
+        # warm-up: the whole run once, so that the decode step is captured for every class of context lengths it passes through
+        infer.generate(prompts, max_new_tokens=new_tokens, temperature=temperature, seed=1, stop_ids=[])
         torch.cuda.synchronize()
         res = infer.generate(prompts, max_new_tokens=new_tokens, temperature=temperature, seed=1, stop_ids=[])
         torch.cuda.synchronize()

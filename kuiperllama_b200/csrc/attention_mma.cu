@@ -42,27 +42,43 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], 
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// 2^x by the special-function unit alone (two units in the last place; 2^-inf = 0): the softmax takes it
+// some ten times per warp and page, where exp2f costs four instructions each.
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// A page of one kv head, [64 keys][HD], into a swizzled stage: the 16-byte chunk c of key row r
-// lands at chunk c ^ (r & 7) of that row.
-template <int HD, int THREADS>
-__device__ __forceinline__ void load_page(bf16* stage, const bf16* __restrict__ src) {
+// SK keys of one kv head, [SK][HD] (a cache page or half of one), into a swizzled stage: the
+// 16-byte chunk c of key row r lands at chunk c ^ (r & 7) of that row.
+template <int HD, int THREADS, int SK>
+__device__ __forceinline__ void load_keys(bf16* stage, const bf16* __restrict__ src) {
     constexpr int CHUNKS = HD / 8;                       // 16-byte chunks per row
     constexpr int ROWS_PER_TURN = THREADS / CHUNKS;      // rows that the CTA covers with one copy per thread
-    static_assert(THREADS % CHUNKS == 0 && ROWS_PER_TURN % 8 == 0 && PAGE % ROWS_PER_TURN == 0, "load_page: thread layout");
-    // A thread keeps its chunk column; its rows are ROWS_PER_TURN apart, a multiple of 8, so the
-    // swizzle term is the same in every turn and the addresses differ by compile-time constants.
+    static_assert(THREADS % CHUNKS == 0 && SK % ROWS_PER_TURN == 0, "load_keys: thread layout");
     const int r0 = threadIdx.x / CHUNKS, c = threadIdx.x % CHUNKS;
-    const uint32_t dst = smem_addr(stage + r0 * HD + ((c ^ (r0 & 7)) << 3));
-    const bf16* from = src + r0 * HD + (c << 3);
+    if constexpr (ROWS_PER_TURN % 8 == 0) {
+        // A thread keeps its chunk column; its rows are a multiple of 8 apart, so the swizzle term is
+        // the same in every turn and the addresses differ by compile-time constants.
+        const uint32_t dst = smem_addr(stage + r0 * HD + ((c ^ (r0 & 7)) << 3));
+        const bf16* from = src + r0 * HD + (c << 3);
 #pragma unroll
-    for (int t = 0; t < PAGE / ROWS_PER_TURN; ++t)
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;"
-                     ::"r"(dst + (uint32_t)(t * ROWS_PER_TURN * HD * 2)), "l"(from + t * ROWS_PER_TURN * HD) : "memory");
+        for (int t = 0; t < SK / ROWS_PER_TURN; ++t)
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;"
+                         ::"r"(dst + (uint32_t)(t * ROWS_PER_TURN * HD * 2)), "l"(from + t * ROWS_PER_TURN * HD) : "memory");
+    } else {
+#pragma unroll
+        for (int t = 0; t < SK / ROWS_PER_TURN; ++t) {
+            const int r = r0 + t * ROWS_PER_TURN;
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;"
+                         ::"r"(smem_addr(stage + r * HD + ((c ^ (r & 7)) << 3))), "l"(src + r * HD + (c << 3)) : "memory");
+        }
+    }
 }
 
 // What a decode step may fold into the attention kernel (one token per sequence): the sum of
@@ -81,8 +97,10 @@ struct DecodeFuse {
     int* counters;                // [rows * KV], zero
 };
 
-template <int HD, int WM, int WN, int NS>
-__global__ void __launch_bounds__(32 * WM * WN, NS == 2 ? ((HD == 64 && WN > 1) ? 4 : 3) : 2)   // NS = 2: three CTAs per SM (168 registers, 3 x 64 KB of stages); four in the decode layout with a head size of 64
+// SK: keys per stage, a cache page (64) or half of one.  Half pages with two warps make a CTA of the
+// decode layout light enough (48 KB of stages at a head size of 128) for four of them on an SM.
+template <int HD, int WM, int WN, int NS, int SK>
+__global__ void __launch_bounds__(32 * WM * WN, SK < PAGE ? 4 : (NS == 2 ? ((HD == 64 && WN > 1) ? 4 : 3) : 2))   // whole pages, NS = 2: three CTAs per SM (168 registers, 3 x 64 KB of stages); four in the decode layout with a head size of 64
 attention_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out,
                      const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                      const int* __restrict__ block_table, int blocks_per_seq,
@@ -96,13 +114,15 @@ attention_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict_
     if (!fuse.enabled) pdl_wait();
     constexpr int THREADS = 32 * WM * WN;
     constexpr int ROWS = 16 * WM;
-    constexpr int KPW = PAGE / WN;                       // keys of a page that one warp handles
+    constexpr int KPW = SK / WN;                         // keys of a stage that one warp handles
+    constexpr int UPP = PAGE / SK;                       // stages ("units") per cache page
+    static_assert(PAGE % SK == 0 && KPW % 16 == 0, "attention_mma_kernel: keys per stage and warp");
     constexpr int NT = KPW / 8;                          // score tiles (8 keys each) per warp
     constexpr int KS = HD / 16;                          // k steps of q . k
     constexpr int ON = HD / 8;                           // output tiles (8 dims each)
     extern __shared__ __align__(128) uint8_t smem_raw[];
-    bf16* k_stage = reinterpret_cast<bf16*>(smem_raw);                   // [NS][64][HD]
-    bf16* v_stage = k_stage + NS * PAGE * HD;                            // [NS][64][HD]
+    bf16* k_stage = reinterpret_cast<bf16*>(smem_raw);                   // [NS][SK][HD]
+    bf16* v_stage = k_stage + NS * SK * HD;                              // [NS][SK][HD]
 
     const int b = blockIdx.y;
     const int g = blockIdx.z % KV, z = blockIdx.z / KV;
@@ -141,17 +161,19 @@ attention_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict_
     const int* table = block_table + (size_t)slot * blocks_per_seq;
     const int full_below = start + t0;                   // keys <= this are visible to every valid row (no window)
 
-    auto issue = [&](int page_idx, int st) {
-        const size_t off = ((size_t)table[page_idx] * KV + g) * PAGE * HD;
-        load_page<HD, THREADS>(k_stage + st * PAGE * HD, k_cache + off);
-        load_page<HD, THREADS>(v_stage + st * PAGE * HD, v_cache + off);
+    // Units of SK keys this CTA reads: its pages, without what lies wholly behind the last position.
+    const int u_begin = p_begin * UPP, u_end = min(p_end * UPP, max_pos / SK + 1);
+    auto issue = [&](int unit, int st) {
+        const size_t off = (((size_t)table[unit / UPP] * KV + g) * PAGE + (unit % UPP) * SK) * HD;
+        load_keys<HD, THREADS, SK>(k_stage + st * SK * HD, k_cache + off);
+        load_keys<HD, THREADS, SK>(v_stage + st * SK * HD, v_cache + off);
         cp_async_commit();
     };
     const bool writes_token = fuse.enabled && p_begin < p_end && p_end == first_page + n_pages;
-    // Pages are requested NS - 1 ahead, one cp.async group per page in page order.  The fused
-    // decode form requests what it can before it waits for the kernel before it: every page but
+    // Units are requested NS - 1 ahead, one cp.async group per unit in key order.  The fused
+    // decode form requests what it can before it waits for the kernel before it: every unit but
     // the one this CTA is about to write the new token into.
-    int next = p_begin, groups = 0;
+    int next = u_begin, groups = 0;
     // The fused form's rotation: cos and sin of the token's position times every frequency, made once per
     // CTA before the wait (position and frequencies are known by then), so that the rotation of q and k
     // costs no sincosf on the path between the kernel ahead and the first page (it took 0.9 us of 7.6 at 8
@@ -159,9 +181,9 @@ attention_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict_
     __shared__ __align__(16) float rot_cs[HD / 2];
     __shared__ __align__(16) float rot_sn[HD / 2];
     if (fuse.enabled) {
-        const int limit = writes_token ? p_end - 1 : p_end;
-        while (groups < NS - 1 && next < limit) { issue(next, (next - p_begin) % NS); ++next; ++groups; }
-        if (threadIdx.x < HD / 2) sincosf((float)(start + t0) * fuse.inv_freq[threadIdx.x], &rot_sn[threadIdx.x], &rot_cs[threadIdx.x]);
+        const int limit = writes_token ? max_pos / SK : u_end;
+        while (groups < NS - 1 && next < limit) { issue(next, (next - u_begin) % NS); ++next; ++groups; }
+        for (int f = threadIdx.x; f < HD / 2; f += THREADS) sincosf((float)(start + t0) * fuse.inv_freq[f], &rot_sn[f], &rot_cs[f]);
         pdl_wait();
         __syncthreads();
     }
@@ -177,74 +199,102 @@ attention_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict_
         constexpr int QI = HD / 8;                       // items per head: HD / 2 pairs, four at a time
         const int n_q = G * QI, n_k = writes_token ? QI : 0, n_v = writes_token ? HD / 4 : 0;
         const size_t dst = writes_token ? (((size_t)table[max_pos / PAGE] * KV + g) * PAGE + (max_pos % PAGE)) * HD : 0;
-        for (int item = threadIdx.x; item < n_q + n_k + n_v; item += THREADS) {
-            const bool is_q = item < n_q, is_k = !is_q && item < n_q + n_k;
-            const int hh = is_q ? item / QI : 0;
-            const int j = is_q ? (item % QI) * 4 : (is_k ? (item - n_q) * 4 : (item - n_q - n_k) * 4);
-            const int col = is_q ? (g * G + hh) * HD + j : (is_k ? (H + g) * HD + j : (H + KV + g) * HD + j);
-            const size_t off = (size_t)(is_q ? row0 + t0 : row0) * width + col;
-            const bool rot = is_q || is_k;
-            float4 x = make_float4(0.f, 0.f, 0.f, 0.f), y = x;
+        // A CTA of fewer than 128 threads takes two items per thread and turn (and four pieces at a time
+        // instead of eight), so that it still waits for memory once.
+        constexpr int IT = THREADS >= 128 ? 1 : 2, PC = 8 / IT;
+        const int n_items = n_q + n_k + n_v;
+        for (int base = 0; base < n_items; base += IT * THREADS) {
+            bool live[IT], is_q[IT], is_k[IT], rot[IT];
+            int hh[IT], j[IT];
+            size_t off[IT];
+            float4 x[IT], y[IT];
+#pragma unroll
+            for (int e = 0; e < IT; ++e) {
+                const int item = base + e * THREADS + threadIdx.x;
+                live[e] = item < n_items;
+                is_q[e] = item < n_q;
+                is_k[e] = !is_q[e] && item < n_q + n_k;
+                hh[e] = is_q[e] ? item / QI : 0;
+                j[e] = is_q[e] ? (item % QI) * 4 : (is_k[e] ? (item - n_q) * 4 : (item - n_q - n_k) * 4);
+                const int col = is_q[e] ? (g * G + hh[e]) * HD + j[e] : (is_k[e] ? (H + g) * HD + j[e] : (H + KV + g) * HD + j[e]);
+                off[e] = (size_t)(is_q[e] ? row0 + t0 : row0) * width + col;
+                rot[e] = is_q[e] || is_k[e];
+                x[e] = y[e] = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
             if (fuse.n_partials == 0) {
-                const uint2 rx = *reinterpret_cast<const uint2*>(fuse.qkv + off);
-                const float2 x01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&rx.x));
-                const float2 x23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&rx.y));
-                x = make_float4(x01.x, x01.y, x23.x, x23.y);
-                if (rot) {
-                    const uint2 ry = *reinterpret_cast<const uint2*>(fuse.qkv + off + HD / 2);
-                    const float2 y01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ry.x));
-                    const float2 y23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ry.y));
-                    y = make_float4(y01.x, y01.y, y23.x, y23.y);
+#pragma unroll
+                for (int e = 0; e < IT; ++e) {
+                    if (!live[e]) continue;
+                    const uint2 rx = *reinterpret_cast<const uint2*>(fuse.qkv + off[e]);
+                    const float2 x01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&rx.x));
+                    const float2 x23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&rx.y));
+                    x[e] = make_float4(x01.x, x01.y, x23.x, x23.y);
+                    if (rot[e]) {
+                        const uint2 ry = *reinterpret_cast<const uint2*>(fuse.qkv + off[e] + HD / 2);
+                        const float2 y01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ry.x));
+                        const float2 y23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ry.y));
+                        y[e] = make_float4(y01.x, y01.y, y23.x, y23.y);
+                    }
                 }
             } else {
-                for (int z0 = 0; z0 < fuse.n_partials; z0 += 8) {      // pieces are added in ascending order
-                    float4 px[8], py[8];
+                for (int z0 = 0; z0 < fuse.n_partials; z0 += PC) {     // pieces are added in ascending order
+                    float4 px[IT][PC], py[IT][PC];
 #pragma unroll
-                    for (int zz = 0; zz < 8; ++zz) {
-                        const float* p = fuse.partials + (size_t)(z0 + zz) * fuse.partial_stride + off;
-                        const bool in = z0 + zz < fuse.n_partials;
-                        px[zz] = in ? __ldcg(reinterpret_cast<const float4*>(p)) : make_float4(0.f, 0.f, 0.f, 0.f);
-                        py[zz] = (in && rot) ? __ldcg(reinterpret_cast<const float4*>(p + HD / 2)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    for (int e = 0; e < IT; ++e) {
+#pragma unroll
+                        for (int zz = 0; zz < PC; ++zz) {
+                            const float* p = fuse.partials + (size_t)(z0 + zz) * fuse.partial_stride + off[e];
+                            const bool in = live[e] && z0 + zz < fuse.n_partials;
+                            px[e][zz] = in ? __ldcg(reinterpret_cast<const float4*>(p)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                            py[e][zz] = (in && rot[e]) ? __ldcg(reinterpret_cast<const float4*>(p + HD / 2)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                        }
                     }
 #pragma unroll
-                    for (int zz = 0; zz < 8; ++zz) {
-                        x.x += px[zz].x; x.y += px[zz].y; x.z += px[zz].z; x.w += px[zz].w;
-                        y.x += py[zz].x; y.y += py[zz].y; y.z += py[zz].z; y.w += py[zz].w;
+                    for (int e = 0; e < IT; ++e) {
+#pragma unroll
+                        for (int zz = 0; zz < PC; ++zz) {
+                            x[e].x += px[e][zz].x; x[e].y += px[e][zz].y; x[e].z += px[e][zz].z; x[e].w += px[e][zz].w;
+                            y[e].x += py[e][zz].x; y[e].y += py[e][zz].y; y[e].z += py[e][zz].z; y[e].w += py[e][zz].w;
+                        }
                     }
                 }
             }
-            uint2 lo_half, hi_half;                      // elements j..j+3 and their partners j + HD / 2 ..
-            if (rot) {
-                float sn[4], cs[4];
-                if (is_q || max_pos == start + t0) {     // a decode step's one token: q and k share the position
-                    const float4 c4 = *reinterpret_cast<const float4*>(rot_cs + j), s4 = *reinterpret_cast<const float4*>(rot_sn + j);
-                    cs[0] = c4.x; cs[1] = c4.y; cs[2] = c4.z; cs[3] = c4.w;
-                    sn[0] = s4.x; sn[1] = s4.y; sn[2] = s4.z; sn[3] = s4.w;
+#pragma unroll
+            for (int e = 0; e < IT; ++e) {
+                if (!live[e]) continue;
+                uint2 lo_half, hi_half;                  // elements j..j+3 and their partners j + HD / 2 ..
+                if (rot[e]) {
+                    float sn[4], cs[4];
+                    if (is_q[e] || max_pos == start + t0) {      // a decode step's one token: q and k share the position
+                        const float4 c4 = *reinterpret_cast<const float4*>(rot_cs + j[e]), s4 = *reinterpret_cast<const float4*>(rot_sn + j[e]);
+                        cs[0] = c4.x; cs[1] = c4.y; cs[2] = c4.z; cs[3] = c4.w;
+                        sn[0] = s4.x; sn[1] = s4.y; sn[2] = s4.z; sn[3] = s4.w;
+                    } else {
+                        const float4 f = *reinterpret_cast<const float4*>(fuse.inv_freq + j[e]);
+                        const float angle = (float)max_pos;
+                        sincosf(angle * f.x, &sn[0], &cs[0]);
+                        sincosf(angle * f.y, &sn[1], &cs[1]);
+                        sincosf(angle * f.z, &sn[2], &cs[2]);
+                        sincosf(angle * f.w, &sn[3], &cs[3]);
+                    }
+                    lo_half.x = pack_bf16(x[e].x * cs[0] - y[e].x * sn[0], x[e].y * cs[1] - y[e].y * sn[1]);
+                    lo_half.y = pack_bf16(x[e].z * cs[2] - y[e].z * sn[2], x[e].w * cs[3] - y[e].w * sn[3]);
+                    hi_half.x = pack_bf16(y[e].x * cs[0] + x[e].x * sn[0], y[e].y * cs[1] + x[e].y * sn[1]);
+                    hi_half.y = pack_bf16(y[e].z * cs[2] + x[e].z * sn[2], y[e].w * cs[3] + x[e].w * sn[3]);
                 } else {
-                    const float4 f = *reinterpret_cast<const float4*>(fuse.inv_freq + j);
-                    const float angle = (float)max_pos;
-                    sincosf(angle * f.x, &sn[0], &cs[0]);
-                    sincosf(angle * f.y, &sn[1], &cs[1]);
-                    sincosf(angle * f.z, &sn[2], &cs[2]);
-                    sincosf(angle * f.w, &sn[3], &cs[3]);
+                    lo_half.x = pack_bf16(x[e].x, x[e].y);
+                    lo_half.y = pack_bf16(x[e].z, x[e].w);
+                    hi_half = lo_half;
                 }
-                lo_half.x = pack_bf16(x.x * cs[0] - y.x * sn[0], x.y * cs[1] - y.y * sn[1]);
-                lo_half.y = pack_bf16(x.z * cs[2] - y.z * sn[2], x.w * cs[3] - y.w * sn[3]);
-                hi_half.x = pack_bf16(y.x * cs[0] + x.x * sn[0], y.y * cs[1] + x.y * sn[1]);
-                hi_half.y = pack_bf16(y.z * cs[2] + x.z * sn[2], y.w * cs[3] + x.w * sn[3]);
-            } else {
-                lo_half.x = pack_bf16(x.x, x.y);
-                lo_half.y = pack_bf16(x.z, x.w);
-                hi_half = lo_half;
-            }
-            if (is_q) {
-                *reinterpret_cast<uint2*>(q_sm + hh * HD + j) = lo_half;
-                *reinterpret_cast<uint2*>(q_sm + hh * HD + j + HD / 2) = hi_half;
-            } else if (is_k) {
-                *reinterpret_cast<uint2*>(fuse.k_cache_w + dst + j) = lo_half;
-                *reinterpret_cast<uint2*>(fuse.k_cache_w + dst + j + HD / 2) = hi_half;
-            } else {
-                *reinterpret_cast<uint2*>(fuse.v_cache_w + dst + j) = lo_half;
+                if (is_q[e]) {
+                    *reinterpret_cast<uint2*>(q_sm + hh[e] * HD + j[e]) = lo_half;
+                    *reinterpret_cast<uint2*>(q_sm + hh[e] * HD + j[e] + HD / 2) = hi_half;
+                } else if (is_k[e]) {
+                    *reinterpret_cast<uint2*>(fuse.k_cache_w + dst + j[e]) = lo_half;
+                    *reinterpret_cast<uint2*>(fuse.k_cache_w + dst + j[e] + HD / 2) = hi_half;
+                } else {
+                    *reinterpret_cast<uint2*>(fuse.v_cache_w + dst + j[e]) = lo_half;
+                }
             }
         }
         __syncthreads();                                 // q_sm is whole; the CTA's own copies below read the new cache rows
@@ -283,17 +333,17 @@ attention_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict_
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 
     while (groups < NS - 1) {
-        if (next < p_end) { issue(next, (next - p_begin) % NS); ++next; } else cp_async_commit();
+        if (next < u_end) { issue(next, (next - u_begin) % NS); ++next; } else cp_async_commit();
         ++groups;
     }
-    for (int pi = p_begin; pi < p_end; ++pi) {
-        const int st = (pi - p_begin) % NS;
-        if (next < p_end) { issue(next, (next - p_begin) % NS); ++next; } else cp_async_commit();
-        cp_async_wait<NS - 1>();                         // all but the NS - 1 newest groups: page pi has landed
+    for (int pi = u_begin; pi < u_end; ++pi) {
+        const int st = (pi - u_begin) % NS;
+        if (next < u_end) { issue(next, (next - u_begin) % NS); ++next; } else cp_async_commit();
+        cp_async_wait<NS - 1>();                         // all but the NS - 1 newest groups: unit pi has landed
         __syncthreads();
-        const bf16* ks_ = k_stage + st * PAGE * HD;
-        const bf16* vs_ = v_stage + st * PAGE * HD;
-        const int key0 = pi * PAGE + warp_n * KPW;       // first key of this warp's share
+        const bf16* ks_ = k_stage + st * SK * HD;
+        const bf16* vs_ = v_stage + st * SK * HD;
+        const int key0 = pi * SK + warp_n * KPW;         // first key of this warp's share
         float s[NT][4];
 #pragma unroll
         for (int n = 0; n < NT; ++n) { s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f; }
@@ -334,7 +384,7 @@ attention_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict_
                 mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
                 const float m_new = fmaxf(m[i], mx[i]);
                 muse[i] = m_new == -INFINITY ? 0.f : m_new;
-                corr[i] = exp2f(m[i] - muse[i]);         // 0 when nothing was seen before
+                corr[i] = fast_exp2(m[i] - muse[i]);     // 0 when nothing was seen before
                 m[i] = m_new;
                 l[i] *= corr[i];
             }
@@ -347,7 +397,7 @@ attention_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict_
             for (int n = 0; n < NT; ++n) {
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
-                    const float p = exp2f(s[n][c] - muse[c >> 1]);
+                    const float p = fast_exp2(s[n][c] - muse[c >> 1]);
                     s[n][c] = p;
                     l[c >> 1] += p;
                 }
@@ -509,7 +559,7 @@ __global__ void attention_mma_combine_kernel(const float* __restrict__ part_o, c
     }
 }
 
-template <int HD, int WM, int WN, int NS>
+template <int HD, int WM, int WN, int NS, int SK = PAGE>
 static int launch_mma(const bf16* q, int q_stride, bf16* out, const bf16* k, const bf16* v, const int* table, int bps,
                       const int* cu, const int* slots, const int* starts, const int* news, float* po, float* pml,
                       int n_seqs, int max_new, int n_rows, int H, int KV, float scale, int window, int S,
@@ -522,14 +572,16 @@ static int launch_mma(const bf16* q, int q_stride, bf16* out, const bf16* k, con
     const int BT = ROWS / Gp;
     const dim3 grid((max_new + BT - 1) / BT, n_seqs, KV * S);
     if (grid.y > 65535 || grid.z > 65535) return KL_ERR_BAD_SIZE;
-    size_t smem = (size_t)2 * NS * PAGE * HD * sizeof(bf16);
+    size_t smem = (size_t)2 * NS * SK * HD * sizeof(bf16);
     if (WN > 1) smem = max(smem, (size_t)(2 * WN * ROWS + WN * ROWS * (HD + 8)) * sizeof(float));
     static bool configured = false;
     if (!configured) {
-        KL_CUDA(cudaFuncSetAttribute(attention_mma_kernel<HD, WM, WN, NS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        KL_CUDA(cudaFuncSetAttribute(attention_mma_kernel<HD, WM, WN, NS, SK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        // all of the SM's memory as shared memory: the kernel's data come through cp.async, and how many CTAs fit decides its speed
+        KL_CUDA(cudaFuncSetAttribute(attention_mma_kernel<HD, WM, WN, NS, SK>, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared));
         configured = true;
     }
-    launch_kernel(attention_mma_kernel<HD, WM, WN, NS>, grid, 32 * WM * WN, smem, stream, q, q_stride, out, k, v, table, bps, cu, slots,
+    launch_kernel(attention_mma_kernel<HD, WM, WN, NS, SK>, grid, 32 * WM * WN, smem, stream, q, q_stride, out, k, v, table, bps, cu, slots,
         starts, news, po, pml, H, KV, Gp, scale * 1.4426950408889634f, window, S, fuse);
     KL_LAUNCH_CHECK();
     if (S > 1 && !fuse.enabled) {
@@ -561,6 +613,10 @@ static int attention_mma_dispatch(const void* q, int q_stride, void* out, const 
     return launch_mma<HD, WM, WN, NS>((const bf16*)q, q_stride, (bf16*)out, (const bf16*)k_cache, (const bf16*)v_cache,     \
                                   block_table, blocks_per_seq, cu_tokens, seq_slots, seq_starts, seq_new, part_o,      \
                                   part_ml, n_seqs, max_new, n_rows, H, KV, scale, window, splits, fuse, stream)
+#define KL_MMA5(HD, WM, WN, NS, SK)                                                                                   \
+    return launch_mma<HD, WM, WN, NS, SK>((const bf16*)q, q_stride, (bf16*)out, (const bf16*)k_cache, (const bf16*)v_cache, \
+                                  block_table, blocks_per_seq, cu_tokens, seq_slots, seq_starts, seq_new, part_o,      \
+                                  part_ml, n_seqs, max_new, n_rows, H, KV, scale, window, splits, fuse, stream)
     // Decode: three CTAs of two stages fit an SM, or two CTAs of three stages.  A CTA's time is set by
     // its chain of pages either way, so what counts is how many rounds of CTAs the grid needs: three
     // stages where they do not add a round (64 sequences of 8 kv heads: 2 rounds both ways, 47 against 53 us).
@@ -569,11 +625,15 @@ static int attention_mma_dispatch(const void* q, int q_stride, void* out, const 
     if (hd == 128 && few_rows) {
         const long long ctas = (long long)n_seqs * KV * splits;
         const long long rounds2 = (ctas + 3 * sms - 1) / (3 * sms), rounds3 = (ctas + 2 * sms - 1) / (2 * sms);
+        // More CTAs than three per SM: light CTAs (two warps, half pages, three stages), four to an SM.
+        static const int light = getenv("KL_ATTN_LIGHT") ? atoi(getenv("KL_ATTN_LIGHT")) : 1;
+        if (rounds2 > 1 && light) KL_MMA5(128, 1, 2, 3, 32);
         if (rounds2 > 1 && rounds3 <= rounds2) KL_MMA(128, 1, 4, 3);
     }
     if (hd == 128) { if (few_rows) KL_MMA(128, 1, 4, 2); else KL_MMA(128, 4, 1, 2); }
     if (hd == 64) { if (few_rows) KL_MMA(64, 1, 4, 2); else KL_MMA(64, 4, 1, 2); }
 #undef KL_MMA
+#undef KL_MMA5
     return KL_ERR_BAD_SIZE;
 }
 

@@ -657,13 +657,32 @@ def _zero_counters(device: torch.device, n: int, use: str = "attention") -> torc
     return have
 
 
-def decode_attention_splits(n_seqs: int, num_kv_heads: int, head_dim: int = 128) -> int:
-    """Pieces a sequence's keys are cut into for the tensor-core decode kernel: as many as keep
-    all CTAs in one round (three CTAs fit an SM, four with a head size of 64), at most 16.  A
-    CTA's time is its chain of pages, so a second round costs more than longer chains (32
-    sequences of 8 kv heads: 27 us with one piece, 35 us with two)."""
-    ctas = max(1, n_seqs * num_kv_heads)
-    return max(1, min(16, ((4 if head_dim == 64 else 3) * sm_count()) // ctas))
+def decode_attention_splits(n_seqs: int, num_kv_heads: int, head_dim: int = 128, context_class: int = 0) -> int:
+    """Pieces a sequence's keys are cut into for the tensor-core decode kernel.
+
+    Up to 1,024 tokens (``context_class`` 0; the engine's class of the longest sequence: 16 pages,
+    then one class per doubling): as many as keep all CTAs in one round (three CTAs fit an SM, four
+    with a head size of 64), at most 16.  A CTA's time is its chain of pages, so a second round
+    costs more than longer chains (32 sequences of 8 kv heads, 512 tokens: 27 us with one piece,
+    35 us with two).  For longer sequences, measured on the 8B shape inside the decode step:
+
+    * where one round has room for two pieces or more per (sequence, kv head) pair: still one
+      round, but up to a piece per four pages (1 sequence of 32,768 tokens: 55 pieces 166 us per
+      layer, 16 pieces 200 us; 2 sequences: 27 pieces 169 us, 16 pieces 197 us);
+    * where it has not, but two pieces per pair fit the light CTAs' round of four per SM: two
+      pieces beyond 4,096 tokens (32 sequences of 8,300 tokens: 307 against 334 us per layer; of
+      2,100 tokens: 192 against 191 us; more pieces in more rounds were never faster)."""
+    pairs = max(1, n_seqs * num_kv_heads)
+    places = (4 if head_dim == 64 else 3) * sm_count()
+    one_round = max(1, places // pairs)
+    if context_class <= 0:
+        return min(16, one_round)
+    pages = 16 << context_class                          # the class's longest sequence
+    if one_round >= 2:
+        return max(1, min(one_round, max(16, pages // 4)))
+    if context_class >= 3 and head_dim == 128 and pairs * 2 <= 4 * sm_count():
+        return 2
+    return 1
 
 
 def decode_fusable(dtype: torch.dtype, head_dim: int, rotary_dim: int, num_heads: int, num_kv_heads: int) -> bool:
@@ -696,7 +715,7 @@ def attention_decode_fused(qkv: torch.Tensor, inv_freq: torch.Tensor, out: torch
     _need(inv_freq.dtype == torch.float32 and inv_freq.numel() == head_dim // 2, "attention_decode_fused: inv_freq")
     _need(all(t.data_ptr() % 16 == 0 for t in (qkv, inv_freq, out, k_cache, v_cache)), "attention_decode_fused: 16-byte aligned operands")
     if splits is None:
-        splits = decode_attention_splits(n, num_kv_heads, head_dim)
+        splits = decode_attention_splits(n, num_kv_heads, head_dim, getattr(step, "context_class", 0))
     po = pml = None
     if splits > 1:
         po = torch.empty((n, num_heads, splits, head_dim), dtype=torch.float32, device=out.device)
@@ -729,7 +748,7 @@ def attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache: torch.
     elif bf and head_dim in MMA_HEAD_DIMS and group <= 16 and (not step.is_decode or DECODE_KERNEL == "mma"):
         splits = 1
         if step.is_decode:
-            splits = decode_attention_splits(step.n_seqs, num_kv_heads, head_dim)
+            splits = decode_attention_splits(step.n_seqs, num_kv_heads, head_dim, getattr(step, "context_class", 0))
         attention_mma(q, q_stride, out, k_cache, v_cache, block_table, step.cu_tokens, step.seq_slots, step.seq_starts,
                       step.seq_new, step.n_seqs, step.max_new, step.n_tokens, num_heads, num_kv_heads, head_dim, scale,
                       window, splits, few_rows=step.is_decode)

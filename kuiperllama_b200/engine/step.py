@@ -76,8 +76,17 @@ class _Staging:
         return self.dev
 
 
+def context_class(max_context: int) -> int:
+    """The class of a step by its longest sequence: 0 up to 16 cache pages, then one class per
+    doubling.  A captured decode step is replayed only for steps of its own class, so a part may
+    plan a decode launch by ``step.context_class`` (into how many pieces it cuts a sequence's keys,
+    say); what it plans by ``max_context`` itself would go stale inside a graph."""
+    pages = -(-max(int(max_context), 1) // PAGE)
+    return max(0, (pages - 1).bit_length() - 4)
+
+
 class _DecodeGraph:
-    """One captured decode step for a fixed number of sequences.  The kernels read their
+    """One captured decode step for a fixed number of sequences and a context class.  The kernels read their
     integer inputs from the engine's staging buffer and the cache's block tables, which keep
     their addresses; a replay runs the step on whatever those hold."""
 
@@ -92,7 +101,7 @@ class Engine:
         self.device = model.runtime.device
         self.use_graphs = use_graphs
         self._staging: Optional[_Staging] = None
-        self._graphs: Dict[int, _DecodeGraph] = {}
+        self._graphs: Dict[Tuple[int, int], _DecodeGraph] = {}        # (sequences, context class) -> captured step
 
     # ------------------------------------------------------------------ slots
     def alloc_slot(self) -> int:
@@ -166,6 +175,7 @@ class Engine:
             seq_slots=take(n_seqs), seq_starts=take(n_seqs), seq_new=take(n_seqs), cu_tokens=take(n_seqs + 1),
             is_decode=all(n == 1 for n in news), max_new=max(news),
             max_context=max(st + n for st, n in zip(starts, news)),
+            context_class=context_class(max(st + n for st, n in zip(starts, news))),
             host_slots=slots, host_starts=starts, host_new=news)
         want_rows = take(n_want)
         return ctx, want_rows, n_want
@@ -188,13 +198,20 @@ class Engine:
         token ids on the host, or an int32 tensor on the device (the sampler's output of the step
         before, which the host need not have seen yet).
 
-        With ``use_graphs`` the step of a batch size is captured in a CUDA graph the first
-        time it runs and replayed afterwards: the same kernels on the same buffers with one
-        launch.  The logits tensor of a replayed step is the graph's own output buffer; it is
-        overwritten by the next decode step of the same batch size."""
+        With ``use_graphs`` the step of a batch size (and of a class of context lengths, see
+        ``context_class``) is captured in a CUDA graph the first time it runs and replayed
+        afterwards: the same kernels on the same buffers with one launch.  The logits tensor of a
+        replayed step is the graph's own output buffer; it is overwritten by the next decode step
+        of the same batch size and class."""
         on_device = isinstance(tokens, torch.Tensor)
         n = len(slots)
-        g = self._graphs.get(n) if self.use_graphs else None
+        key, g = None, None
+        if self.use_graphs:
+            try:
+                key = (n, context_class(max(self.cache.lengths[s] for s in slots) + 1))
+            except (IndexError, KeyError, TypeError, ValueError):
+                key = (n, 0)                                  # a bad slot: the ordinary path below says so
+            g = self._graphs.get(key)
         if g is not None and self._staging is not None and g.staging_ptr == self._staging.dev.data_ptr():
             return self._replay(g, list(slots), tokens if on_device else [int(t) for t in tokens])
         if on_device:
@@ -220,7 +237,7 @@ class Engine:
                 static_logits = self.model.logits(r2, p2, want_rows)
             captured = ops.launch_count - before
             ops.launch_count = before                     # captured calls are not launches; replays are counted below
-            self._graphs[n] = _DecodeGraph(graph, static_logits, self._staging.dev.data_ptr(), captured)
+            self._graphs[(n, ctx.context_class)] = _DecodeGraph(graph, static_logits, self._staging.dev.data_ptr(), captured)
         else:
             g.graph.replay()
             ops.launch_count += g.launches
@@ -228,6 +245,10 @@ class Engine:
         for s, st in zip(inputs, ctx.host_starts):
             self.cache.lengths[s.slot] = st + 1
         return logits
+
+    def graph_sizes(self) -> List[int]:
+        """The batch sizes whose decode step has been captured (in any context class)."""
+        return sorted({n for n, _ in self._graphs})
 
     def _replay(self, g: _DecodeGraph, slots: List[int], tokens) -> torch.Tensor:
         """The short way through a decode step whose graph exists: the same checks and the same

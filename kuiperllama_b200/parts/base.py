@@ -52,6 +52,10 @@ class StepContext:
     host_slots: List[int]         # host copies for parts that plan their launches
     host_starts: List[int]
     host_new: List[int]
+    # The engine's class of max_context (0 up to 16 cache pages, then one per doubling).  A captured
+    # decode step is replayed for steps of its class only, so a decode launch may be planned by this
+    # number; a plan made from max_context itself would go stale inside a graph.
+    context_class: int = 0
     # Set by the block around a call of a mixer or feed-forward that says it ``may_accumulate``:
     # the float32 residual stream its result is to be added to, with the norm that will read the
     # stream next.  Such a part may add the result itself (inside its last product) and return

@@ -171,7 +171,7 @@ def test_all_32_layers_in_bfloat16_against_the_float32_path(full_models):
         assert_close(tail[0], ref[n_head:n_head + 1], "bfloat16", "8B first decoded token at context 3,018", layers=32, stream="wide")
         assert_close(torch.cat(tail), ref[n_head:], "bfloat16", "8B last 32 one by one past 3,000 tokens", layers=32, stream="wide")
         _assert_rows_noise(torch.cat(tail), ref[n_head:], "8B last 32 one by one past 3,000 tokens")
-        assert sorted(engine._graphs) == [1]
+        assert engine.graph_sizes() == [1]
 
         # (3) batches of 8 unequal requests through graphs; shorter ones end earlier; a second batch on their slots
         lengths1 = [(130, 100), (700, 690), (64, 40), (333, 320), (90, 89), (210, 180), (41, 33), (500, 470)]
@@ -188,7 +188,7 @@ def test_all_32_layers_in_bfloat16_against_the_float32_path(full_models):
                              layers=32, stream="wide")
                 _assert_rows_noise(got[i][want], ref_rows, f"8B batch {b} request {i}")
         assert set(used[0]) == set(used[1]), "the second batch did not run on the first one's slots"
-        assert 8 in engine._graphs and 1 in engine._graphs
+        assert {1, 8} <= set(engine.graph_sizes())
         assert engine.cache.slots.held() == 0 and engine.cache.pages_held() == [0]
         engine.check_device_errors()
         oracle_engine.check_device_errors()

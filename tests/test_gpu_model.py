@@ -267,7 +267,7 @@ def test_decode_steps_replayed_from_cuda_graphs(model_folders, name, dtype):
                 live = [i for i in live if done[i] < len(reqs[i])]
             for i, r in enumerate(reqs):
                 assert_close(torch.stack(got[i]), plain_logits(folder, r)[shape[i][1]:], dtype, f"{name} graphs batch {batch} request {i}")
-        assert sorted(engine._graphs) == [1, 2, 3]
+        assert engine.graph_sizes() == [1, 2, 3]
         from kuiperllama_b200.csrc import ops
         ops.check_status(torch.device("cuda:0"))
 

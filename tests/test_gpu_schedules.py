@@ -143,11 +143,44 @@ def test_graph_decode_at_larger_batches(models, name, batch):
             for s in slots:
                 engine.free_slot(s)
         outs[use_graphs] = torch.stack(rows, dim=1)          # [batch, steps, vocab]
-        assert (sorted(engine._graphs) == [batch]) == use_graphs
+        assert (engine.graph_sizes() == [batch]) == use_graphs
         engine.check_device_errors()
     assert torch.equal(outs[True], outs[False]), "a replayed graph gave other logits than the same kernels launched one by one"
     for i in sorted({0, 1, batch // 2, batch - 2, batch - 1}):
         assert_close(outs[True][i], plain_logits(folder, reqs[i])[-steps:], "bfloat16", f"{name} graph decode, sequence {i} of {batch}", **WIDE)
+
+
+@pytest.mark.parametrize("name", CONFIGS)
+def test_graph_decode_crosses_a_context_class(model_folders, name):
+    """A sequence grows past 1,024 tokens while it decodes: the step is captured once more for the
+    next class of context lengths (its decode attention is cut into other pieces there), and the
+    logits on both sides of the border agree with the plain implementation and with the same
+    steps launched kernel by kernel."""
+    from kuiperllama_b200.engine import Engine, SequenceInput, load_model
+    from kuiperllama_b200.engine.step import context_class
+    assert [context_class(n) for n in (1, 1024, 1025, 2048, 2049, 4096, 4097)] == [0, 0, 1, 1, 2, 2, 3]
+    folder = model_folders(name, seed=SEEDS[name], std=SHARP, max_position_embeddings=2304)
+    vocab = config_dict(name)["vocab_size"]
+    steps = 12
+    reqs = [random_tokens(n + steps, vocab, seed=2500 + n) for n in (1018, 300)]
+    outs = {}
+    with torch.inference_mode():
+        model = load_model(folder, dtype="bfloat16", device="cuda:0")
+        for use_graphs in (False, True):
+            engine = Engine(model, model.new_cache(max_tokens=64 * 24), use_graphs=use_graphs)
+            slots = [engine.alloc_slot() for _ in reqs]
+            for s, r in zip(slots, reqs):
+                engine.step([SequenceInput(s, r[:-steps], [])])
+            rows = [engine.decode_step(slots, [r[len(r) - steps + k] for r in reqs]).clone() for k in range(steps)]
+            outs[use_graphs] = torch.stack(rows, dim=1)              # [2, steps, vocab]
+            if use_graphs:
+                assert sorted(engine._graphs) == [(2, 0), (2, 1)]
+            engine.check_device_errors()
+    assert torch.equal(outs[True], outs[False]), "replayed steps gave other logits than the same kernels launched one by one"
+    for i, r in enumerate(reqs):
+        ref = plain_logits(folder, r)[-steps:]
+        for use_graphs in (False, True):
+            assert_close(outs[use_graphs][i], ref, "bfloat16", f"{name} across the class border, graphs {use_graphs}, request {i}", **WIDE)
 
 
 @pytest.mark.parametrize("n_seqs", [3, 4])
