@@ -742,7 +742,17 @@ KL_API int kl_gemm_tcgen05_skinny(const void* a, long long lda, const void* w, l
     GemmArgs args{out, ldo, (long long)M * ldo, N, M, k_blocks, out_f32, status, 0, 0, swiglu,
                   scale_ss, scale_ss_n, scale_eps, K, sink, sink_ss, sink_counters, sink_w, (__nv_bfloat16*)sink_scaled};
     dim3 grid((N + TC_BM - 1) / TC_BM, 1, splits);
-    // two CTAs share an SM so that one's epilogue overlaps the other's loads
+    // A grid of at most one CTA per SM (small matrices) gives each CTA the whole of the SM's shared
+    // memory as stages: what a CTA has in flight bounds what it streams (96 KB over the 1.5 us a tile
+    // takes to arrive are 64 GB/s).  Otherwise two CTAs share an SM, so that one's epilogue overlaps
+    // the other's loads.
+    const int sms = kl::sm_count();
+    if (sms <= 0) return KL_ERR_SETUP;
+    if ((long long)grid.x * splits <= sms) {
+        if (bn == 16) return launch<16, 12, true>(ma, mb, args, grid, stream);
+        if (bn == 32) return launch<32, 10, true>(ma, mb, args, grid, stream);
+        return launch<64, 8, true>(ma, mb, args, grid, stream);
+    }
     if (bn == 16) return launch<16, 6, true>(ma, mb, args, grid, stream);
     if (bn == 32) return launch<32, 5, true>(ma, mb, args, grid, stream);
     return launch<64, 4, true>(ma, mb, args, grid, stream);
