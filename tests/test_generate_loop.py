@@ -162,3 +162,30 @@ def test_default_cache_size_fits_the_device_not_the_configuration():
     # a small model keeps the size it asked for; no room at all still gives one page
     assert default_cache_tokens(1024, max_batch=4, max_seq_len=100, free_bytes=free) == 4 * 2 * PAGE
     assert default_cache_tokens(per_token, 64, 131072, free_bytes=1000) == PAGE
+
+
+def test_context_classes_and_the_pieces_planned_by_them(monkeypatch):
+    """The class of a step's longest sequence (what a captured decode step is keyed by) and the number of
+    pieces the decode attention cuts a sequence into for it: never more CTAs than one round holds where
+    pieces are cut at all, never fewer pieces for a longer context, and one piece where the pairs of
+    (sequence, kv head) fill the machine by themselves."""
+    from kuiperllama_b200.csrc import ops
+    from kuiperllama_b200.engine.step import context_class
+    assert [context_class(n) for n in (0, 1, PAGE * 16, PAGE * 16 + 1, PAGE * 32, PAGE * 32 + 1, 131072)] == [0, 0, 0, 1, 1, 2, 7]
+    monkeypatch.setattr(ops, "sm_count", lambda: 148)
+    for head_dim, per_sm in ((128, 3), (64, 4)):
+        for kv in (1, 4, 8, 32):
+            for n_seqs in (1, 2, 3, 8, 16, 31, 32, 37, 64, 200):
+                pieces = [ops.decode_attention_splits(n_seqs, kv, head_dim, c) for c in range(9)]
+                assert pieces == sorted(pieces) and pieces[0] >= 1, (head_dim, kv, n_seqs, pieces)
+                pairs = n_seqs * kv
+                for c, s in enumerate(pieces):
+                    if s > 2:
+                        assert pairs * s <= per_sm * 148, (head_dim, kv, n_seqs, c, s)
+                    if s == 2:
+                        assert pairs * s <= 4 * 148
+                if pairs > 2 * 148:
+                    assert pieces[-1] == 1
+    assert ops.decode_attention_splits(8, 8, 128, 0) == 6 and ops.decode_attention_splits(8, 8, 128, 5) == 6
+    assert ops.decode_attention_splits(1, 8, 128, 0) == 16 and ops.decode_attention_splits(1, 8, 128, 5) == 55
+    assert ops.decode_attention_splits(32, 8, 128, 2) == 1 and ops.decode_attention_splits(32, 8, 128, 3) == 2
