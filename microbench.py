@@ -6,6 +6,9 @@ repeats, a buffer larger than L2 written between repeats), and print the achieve
     python microbench.py attention_prefill --tokens 2048 --heads 32 --kv-heads 8 --head-dim 128 [--mma]
     python microbench.py attention_decode --batch 64 --context 640 --heads 32 --kv-heads 8 --head-dim 128
     python microbench.py attention_decode --batch 8 --context 516 --fused     (the decode step's form)
+    python microbench.py decode_step --shape 8b --layers 4 --batch 32 --context 8300 [--splits 2]
+        (decode steps of a few layers of one of bench.py's shapes, replayed from a CUDA graph; --splits
+        fixes the number of pieces the decode attention cuts a sequence into, else the package's rule)
 
 It is also the small case that profiler captures of single kernels are taken on.
 """
@@ -53,9 +56,50 @@ def _paged(n_seqs: int, length: int, kv: int, hd: int):
     return table, k, v
 
 
+def _decode_step(args) -> int:
+    import bench
+    import kuiperllama_b200 as kl
+    from kuiperllama_b200.config import config_from_dict
+    from kuiperllama_b200.engine import Engine, SequenceInput
+    from kuiperllama_b200.engine.step import context_class
+    base = {"8b": bench.LLAMA31_8B, "7b": bench.LLAMA2_7B, "1b": bench.LLAMA32_1B}[args.shape]
+    B, N, L = args.batch, args.context, args.layers
+    cfg = dict(base, num_hidden_layers=L, max_position_embeddings=max(base["max_position_embeddings"], N + args.steps + 16))
+    model = kl.random_model(config_from_dict(cfg), seed=0)
+    rule = ops.decode_attention_splits
+    if args.splits:
+        ops.decode_attention_splits = lambda n_seqs, kv, hd=128, cls=0: args.splits
+    g = torch.Generator().manual_seed(1)
+    room = N + args.steps + 16
+    eng = Engine(model, model.new_cache(max_tokens=B * (room + ops.PAGE), max_seq_len=room), use_graphs=True)
+    with torch.inference_mode():
+        slots = [eng.alloc_slot() for _ in range(B)]
+        for s in slots:                                   # one prompt per step keeps the prefill's activations small
+            eng.step([SequenceInput(s, torch.randint(0, cfg["vocab_size"], (N,), generator=g).tolist(), [])])
+        tok = [1] * B
+        for _ in range(6):
+            eng.decode_step(slots, tok)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(args.steps):
+            eng.decode_step(slots, tok)
+        b.record()
+        torch.cuda.synchronize()
+    eng.check_device_errors()
+    us = a.elapsed_time(b) / args.steps * 1e3
+    pieces = args.splits or rule(B, cfg["num_key_value_heads"], cfg["hidden_size"] // cfg["num_attention_heads"], context_class(N + 6))
+    print(json.dumps({"kernel": "decode_step", "shape": args.shape, "layers": L, "batch": B, "context": N, "pieces": pieces,
+                      "us_per_step": round(us, 1), "us_per_layer": round(us / L, 1)}))
+    return 0
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="microbench")
-    ap.add_argument("kernel", choices=["gemm_skinny", "gemm_tcgen05", "attention_prefill", "attention_decode"])
+    ap.add_argument("kernel", choices=["gemm_skinny", "gemm_tcgen05", "attention_prefill", "attention_decode", "decode_step"])
+    ap.add_argument("--shape", default="8b", choices=["8b", "7b", "1b"], help="decode_step: which of bench.py's shapes")
+    ap.add_argument("--layers", type=int, default=4, help="decode_step: layers of the model")
+    ap.add_argument("--steps", type=int, default=150, help="decode_step: timed steps")
     ap.add_argument("--m", type=int, default=8)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
@@ -75,6 +119,8 @@ def main(argv=None) -> int:
     args = ap.parse_args(argv)
     torch.manual_seed(0)
     out = {"kernel": args.kernel}
+    if args.kernel == "decode_step":
+        return _decode_step(args)
     if args.kernel in ("gemm_skinny", "gemm_tcgen05"):
         a = torch.randn(args.m, args.k, device=DEV).bfloat16()
         w = torch.randn(args.n, args.k, device=DEV).bfloat16()
