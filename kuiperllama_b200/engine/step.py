@@ -95,6 +95,10 @@ class _DecodeGraph:
 
 
 class Engine:
+    # A captured step keeps its own activations and logits (64 sequences of a 128k vocabulary: 33 MB);
+    # beyond this many the one replayed longest ago is dropped and captured again if it comes back.
+    MAX_GRAPHS = 48
+
     def __init__(self, model: DecoderModel, cache: SequenceCache, use_graphs: bool = False):
         self.model = model
         self.cache = cache
@@ -212,6 +216,8 @@ class Engine:
             except (IndexError, KeyError, TypeError, ValueError):
                 key = (n, 0)                                  # a bad slot: the ordinary path below says so
             g = self._graphs.get(key)
+            if g is not None:
+                self._graphs[key] = self._graphs.pop(key)     # most recently used last
         if g is not None and self._staging is not None and g.staging_ptr == self._staging.dev.data_ptr():
             return self._replay(g, list(slots), tokens if on_device else [int(t) for t in tokens])
         if on_device:
@@ -238,6 +244,8 @@ class Engine:
             captured = ops.launch_count - before
             ops.launch_count = before                     # captured calls are not launches; replays are counted below
             self._graphs[(n, ctx.context_class)] = _DecodeGraph(graph, static_logits, self._staging.dev.data_ptr(), captured)
+            while len(self._graphs) > self.MAX_GRAPHS:
+                self._graphs.pop(next(iter(self._graphs)))
         else:
             g.graph.replay()
             ops.launch_count += g.launches

@@ -272,6 +272,39 @@ def test_decode_steps_replayed_from_cuda_graphs(model_folders, name, dtype):
         ops.check_status(torch.device("cuda:0"))
 
 
+def test_captured_steps_beyond_the_limit_are_dropped_and_captured_again(model_folders):
+    """With room for two captured steps, batches of 3, 2 and 1 sequences (twice) keep dropping the
+    graph used longest ago and capturing it anew; the logits stay those of the plain implementation."""
+    from kuiperllama_b200.engine import Engine, SequenceInput, load_model
+    folder = model_folders("tiny3", seed=2)
+    vocab = config_dict("tiny3")["vocab_size"]
+    with torch.inference_mode():
+        model = load_model(folder, dtype="bfloat16", device="cuda:0")
+        engine = Engine(model, model.new_cache(max_tokens=64 * 12), use_graphs=True)
+        engine.MAX_GRAPHS = 2
+        for batch in range(2):
+            shape = [(40, 30), (37, 30), (34, 30)]
+            reqs = [random_tokens(n, vocab, seed=900 + 10 * batch + i) for i, (n, _) in enumerate(shape)]
+            slots = [engine.alloc_slot() for _ in reqs]
+            engine.step([SequenceInput(s, r[:p], []) for s, r, (_, p) in zip(slots, reqs, shape)])
+            done = [p for _, p in shape]
+            live = [0, 1, 2]
+            got = [[] for _ in reqs]
+            while live:
+                logits = engine.decode_step([slots[i] for i in live], [reqs[i][done[i]] for i in live]).clone()
+                assert len(engine._graphs) <= 2
+                for j, i in enumerate(live):
+                    got[i].append(logits[j])
+                    done[i] += 1
+                for i in [i for i in live if done[i] == len(reqs[i])]:
+                    engine.free_slot(slots[i])
+                live = [i for i in live if done[i] < len(reqs[i])]
+            assert engine.graph_sizes() == [1, 2]
+            for i, r in enumerate(reqs):
+                assert_close(torch.stack(got[i]), plain_logits(folder, r)[shape[i][1]:], "bfloat16", f"tiny3 two graphs kept, batch {batch} request {i}")
+        engine.check_device_errors()
+
+
 def test_a_float16_checkpoint_in_a_float32_run_keeps_its_values(tmp_path, model_folders):
     """A folder stored in float16 (as Llama-2 checkpoints are): the float32 run uses exactly those
     values, not values rounded to bfloat16 on the way; the bfloat16 run rounds them once."""
