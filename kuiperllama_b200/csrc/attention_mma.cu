@@ -8,14 +8,19 @@
 //
 // A CTA owns 16 * WM query rows of one sequence and one kv head; a row is (token, head of the
 // kv group), so the group's heads share every key and value that is loaded.  Keys and values
-// come a cache page (64 keys) at a time through cp.async into a ring of shared-memory stages
-// (two here; the count is a template parameter), XOR-swizzled so that ldmatrix is free of bank conflicts.  Each warp keeps its
+// come a cache page (64 keys) or half a page at a time through cp.async into a ring of
+// shared-memory stages (NS stages of SK keys: template parameters), XOR-swizzled so that
+// ldmatrix is free of bank conflicts.  Each warp keeps its
 // 16 rows' queries as mma.sync A fragments, multiplies them with the page's keys (B fragments
 // by ldmatrix), runs the online softmax on the score fragments in registers, and multiplies
 // the probabilities (converted in place to A fragments) with the values (ldmatrix.trans).
-// With WN > 1 (decode: few rows) the warps of a CTA split each page's keys instead of the
+// With WN > 1 (decode: few rows) the warps of a CTA split each stage's keys instead of the
 // rows and merge their results in shared memory; with splits > 1 the pages of a sequence are
-// cut over blockIdx.z and a second kernel merges the pieces.
+// cut over blockIdx.z and the pieces are merged by a second kernel or, in the decode step's
+// fused form, by the last CTA of the sequence to finish.  The decode layout comes as four warps
+// on whole pages (two stages, three CTAs per SM; or three stages, two per SM) and as light CTAs
+// of two warps on half pages (three stages of 16 KB at a head size of 128: four CTAs per SM),
+// taken where three per SM would leave CTAs for a second round.
 #include "common.cuh"
 
 namespace kl {
