@@ -158,7 +158,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     // SM walks many tiles; weights-as-rows: the grid has one CTA per tile).
     const int n_tiles = WEIGHT_ROWS ? (int)gridDim.x : args.tiles_m * args.tiles_n;
     auto tile_at = [&](int t, int& ta, int& tb) {
-        if constexpr (WEIGHT_ROWS) { ta = t; tb = 0; }
+        // weights-as-rows: tiles_m token tiles of BN tokens per weight tile, neighbours in the grid, so
+        // that the CTAs that share a weight tile ask for it at about the same time (one trip to HBM)
+        if constexpr (WEIGHT_ROWS) { ta = t / args.tiles_m; tb = t - ta * args.tiles_m; }
         else tile_of(t, args.tiles_m, args.tiles_n, ta, tb);
     };
     // k range of this CTA (cut over blockIdx.z)
@@ -260,14 +262,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         // ---------------------------------------------------------------- epilogue: warps 2..5
         const int quarter = warp & 3;                         // the 32 tensor-memory lanes this warp may read
         pdl_wait();                                           // before this grid writes anything
-        __shared__ float inv_rms[64];                         // weights-as-rows: the factor of every token (column)
+        constexpr int TOKENS = BN > 64 ? BN : 64;
+        static_assert(!WEIGHT_ROWS || TOKENS <= 128, "one epilogue thread per token sets its factor");
+        __shared__ float inv_rms[TOKENS];                     // weights-as-rows: the factor of every token (column)
         if constexpr (WEIGHT_ROWS) {
             const int et = threadIdx.x - 64;                  // 0..127 among the epilogue threads
-            if (et < 64) {
+            if (et < TOKENS) {
                 float f = 1.0f;
                 if (args.scale_ss != nullptr) {
                     float ss = 0.f;
-                    if (et < args.rows_b)
+                    if (et < args.rows_b && et < 64)
                         for (int j = 0; j < args.scale_ss_n; ++j) ss += args.scale_ss[j * 64 + et];
                     f = rsqrtf(ss / (float)args.K + args.scale_eps);
                 }
@@ -321,9 +325,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         if (feature < args.rows_a / 2) {
 #pragma unroll
                             for (int j = 0; j < 16; ++j) {
-                                const int m = c + j;
-                                if (m < args.rows_b)
-                                    outb[(size_t)m * args.ld_out + feature] =
+                                const int m = c + j, token = tile_b * BN + m;
+                                if (token < args.rows_b)
+                                    outb[(size_t)token * args.ld_out + feature] =
                                         __float2bfloat16_rn(silu_mul(__uint_as_float(r[j]) * inv_rms[m], xch[m * 64 + f]));
                             }
                         }
@@ -341,15 +345,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
                         for (int j = 0; j < 16; ++j) r[j] = 0u;
                     }
+                    const int token0 = tile_b * BN + c;
                     if (row < args.rows_a && args.out_f32) {
 #pragma unroll
                         for (int j = 0; j < 16; ++j)
-                            if (c + j < args.rows_b) out[(size_t)(c + j) * args.ld_out + row] = __uint_as_float(r[j]) * inv_rms[c + j];
+                            if (token0 + j < args.rows_b) out[(size_t)(token0 + j) * args.ld_out + row] = __uint_as_float(r[j]) * inv_rms[c + j];
                     } else if (row < args.rows_a) {
 #pragma unroll
                         for (int j = 0; j < 16; ++j)
-                            if (c + j < args.rows_b)
-                                outb[(size_t)(c + j) * args.ld_out + row] = __float2bfloat16_rn(__uint_as_float(r[j]) * inv_rms[c + j]);
+                            if (token0 + j < args.rows_b)
+                                outb[(size_t)(token0 + j) * args.ld_out + row] = __float2bfloat16_rn(__uint_as_float(r[j]) * inv_rms[c + j]);
                     }
                 }
             }
@@ -708,7 +713,8 @@ KL_API int kl_gemm_tcgen05(const void* a, long long lda, const void* w, long lon
     return launch<256, 4, false>(ma, mb, args, grid, stream);
 }
 
-// Few tokens (M <= 64): weights as tile rows, the K range cut into `splits` pieces.
+// Few tokens (M <= 512): weights as tile rows (beyond 64 tokens: up to four tiles of 128 tokens per
+// weight tile), the K range cut into `splits` pieces.
 // splits == 1: out[M, N] directly (bf16 or float32).  splits > 1: out is float32
 // [splits, M, N] partial sums (out_f32 must be 1) for the caller to add.
 //
@@ -725,7 +731,8 @@ KL_API int kl_gemm_tcgen05_skinny(const void* a, long long lda, const void* w, l
                                   int scale_ss_n, float scale_eps, float* sink, float* sink_ss, int* sink_counters,
                                   const float* sink_w, void* sink_scaled, int* status, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return KL_OK;
-    if (M > 64) return KL_ERR_BAD_SIZE;
+    if (M > 512) return KL_ERR_BAD_SIZE;
+    if (M > 64 && (scale_ss != nullptr || sink != nullptr)) return KL_ERR_BAD_SIZE;     // the folded norm: one tile of tokens
     if (swiglu && (splits != 1 || out_f32 || N % 128)) return KL_ERR_BAD_SIZE;
     if (!aligned_operand(w, ldw, K) || !aligned_operand(a, lda, K)) return KL_ERR_BAD_ALIGN;
     if (scale_ss != nullptr && scale_ss_n < 1) return KL_ERR_BAD_SIZE;
@@ -734,14 +741,18 @@ KL_API int kl_gemm_tcgen05_skinny(const void* a, long long lda, const void* w, l
     const int k_blocks = (K + TC_BK - 1) / TC_BK;
     if (splits < 1 || splits > k_blocks || splits > 65535) return KL_ERR_BAD_SIZE;
     if (splits > 1 && !out_f32) return KL_ERR_BAD_DTYPE;
-    const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+    // More than 64 tokens: tiles of 128 tokens (a stage holds 16 KB of weights and 16 KB of tokens; with
+    // two tiles of 64 tokens side by side the weights cross from L2 to the SMs twice).  KL_SKINNY_BN128=0: tiles of 64.
+    static const int wide = getenv("KL_SKINNY_BN128") ? atoi(getenv("KL_SKINNY_BN128")) : 1;
+    const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : ((M <= 64 || !wide) ? 64 : 128));
     CUtensorMap ma, mb;
     int rc;
     if ((rc = make_map(&ma, w, N, K, ldw, TC_BM)) != KL_OK) return rc;
     if ((rc = make_map(&mb, a, M, K, lda, bn)) != KL_OK) return rc;
-    GemmArgs args{out, ldo, (long long)M * ldo, N, M, k_blocks, out_f32, status, 0, 0, swiglu,
+    const int token_tiles = (M + bn - 1) / bn;
+    GemmArgs args{out, ldo, (long long)M * ldo, N, M, k_blocks, out_f32, status, token_tiles, 0, swiglu,
                   scale_ss, scale_ss_n, scale_eps, K, sink, sink_ss, sink_counters, sink_w, (__nv_bfloat16*)sink_scaled};
-    dim3 grid((N + TC_BM - 1) / TC_BM, 1, splits);
+    dim3 grid(((N + TC_BM - 1) / TC_BM) * token_tiles, 1, splits);
     // A grid of at most one CTA per SM (small matrices) gives each CTA the whole of the SM's shared
     // memory as stages: what a CTA has in flight bounds what it streams (96 KB over the 1.5 us a tile
     // takes to arrive are 64 GB/s).  Otherwise two CTAs share an SM, so that one's epilogue overlaps
@@ -751,8 +762,10 @@ KL_API int kl_gemm_tcgen05_skinny(const void* a, long long lda, const void* w, l
     if ((long long)grid.x * splits <= sms) {
         if (bn == 16) return launch<16, 12, true>(ma, mb, args, grid, stream);
         if (bn == 32) return launch<32, 10, true>(ma, mb, args, grid, stream);
-        return launch<64, 8, true>(ma, mb, args, grid, stream);
+        if (bn == 64) return launch<64, 8, true>(ma, mb, args, grid, stream);
+        return launch<128, 6, true>(ma, mb, args, grid, stream);
     }
+    if (bn == 128) return launch<128, 3, true>(ma, mb, args, grid, stream);
     if (bn == 16) return launch<16, 6, true>(ma, mb, args, grid, stream);
     if (bn == 32) return launch<32, 5, true>(ma, mb, args, grid, stream);
     return launch<64, 4, true>(ma, mb, args, grid, stream);

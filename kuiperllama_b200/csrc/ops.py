@@ -361,7 +361,7 @@ def skinny_splits(N: int, K: int, M: int = 1) -> int:
     Every piece is written as float32 [M, N] and read again by the kernel that adds the pieces, so
     with many tokens and a short k range fewer pieces are better: their bytes stay under a quarter
     of the weights' (pieces * M * 4 <= K * 2 / 4)."""
-    tiles = (N + 127) // 128
+    tiles = ((N + 127) // 128) * max(1, (M + 127) // 128)    # CTAs per cut: weight tiles x token tiles (of 128 beyond 64 tokens)
     k_blocks = (K + 63) // 64
     want = max(1, min((2 * sm_count() + tiles // 2) // tiles, k_blocks // 4, 32, max(1, K // (8 * max(M, 1)))))
     per = (k_blocks + want - 1) // want
@@ -459,12 +459,36 @@ def gemm_skinny_stream(w: torch.Tensor, a: torch.Tensor, row_scale=None, sink=No
     return result
 
 
+# Which way round a product of M tokens and N features runs.  Weights as tile rows (tiles of 128
+# features x 16 to 128 tokens, the K range cut so that all SMs stream): every weight crosses from HBM
+# once and 16 KB of it per CTA and k block.  Tokens as tile rows (128 x 256 or 256 x 256): both operands
+# are reused, but a product of 128 tokens and 4,096 features has 16 tiles for 148 SMs (8B shape, 96
+# sequences: 7.6 ms per decode step that way, 5.5 ms with weights as rows).  Measured per product on
+# the 8B shape, us with tokens / weights as rows:
+#   128 tokens: q/k/v (24 tiles) 29.2 / 18.2, output (16) 26.7 / 13.9, gate/up (112) 43.1 / 53.6, down (16) 82.9 / 28.9
+#   384 tokens: q/k/v (72) 29.6 / 23.2, output (48) 26.8 / 21.7, gate/up (336) 85.0 / -, down (48) 82.6 / 46.1
+#   512 tokens: q/k/v (96) 27.6 / 34.1, output (64) 24.2 / 21.9, down (64) 70.2 / 58.5
+# and on the 1B shape at 128 tokens: gate/up (64 tiles) 18.0 / 25.9.  So beyond 64 tokens: weights as rows
+# while the other way has fewer tiles than 0.6 of the SMs; the gate/up product, whose K range cannot be
+# cut (its epilogue needs whole sums), while it has fewer than a third of them.
+SKINNY_MAX_ROWS = 512
+
+
+def weights_as_rows(M: int, N: int, swiglu: bool = False) -> bool:
+    if M <= 64:
+        return True
+    if M > SKINNY_MAX_ROWS:
+        return False
+    tiles = ((M + 127) // 128) * ((N + 255) // 256)
+    return tiles * 3 < sm_count() if swiglu else tiles * 5 < sm_count() * 3
+
+
 def gemm_skinny_partials(a: torch.Tensor, w: torch.Tensor, splits: Optional[int] = None) -> Optional[torch.Tensor]:
-    """The pieces of a @ w^T for M <= 64 tokens as float32 [S, M, N], for a consumer that adds
+    """The pieces of a @ w^T for few tokens (``weights_as_rows``) as float32 [S, M, N], for a consumer that adds
     them itself (the norm after a projection, the rotary kernel after q/k/v); None when the
     product is not cut (S == 1) or the operands do not fit the tensor-core kernel."""
     (M, K), (N, K2) = a.shape, w.shape
-    if M > 64 or a.dtype != torch.bfloat16 or K != K2:
+    if not weights_as_rows(M, N) or a.dtype != torch.bfloat16 or K != K2:
         return None
     probe = torch.empty((0, N), dtype=torch.float32, device=a.device)
     if not _tc_ok(a, w, probe):
@@ -482,13 +506,13 @@ def gemm_skinny_partials(a: torch.Tensor, w: torch.Tensor, splits: Optional[int]
 
 def gemm_skinny(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, splits: Optional[int] = None,
                 swiglu: bool = False) -> None:
-    """out[M, N] = a @ w^T for M <= 64 tokens: weights as tile rows, each weight read once, the
+    """out[M, N] = a @ w^T for M <= SKINNY_MAX_ROWS tokens: weights as tile rows, each weight read once, the
     K range cut into ``splits`` pieces whose float32 partial sums are added in a fixed order.
     With ``swiglu`` (rows of ``w`` alternate 64 gate and 64 up rows; no cut) out[M, N / 2]
     receives silu(gate) * up."""
     _cuda(a, w, out)
     (M, K), (N, K2) = a.shape, w.shape
-    _need(K == K2 and out.shape[0] >= M and out.shape[1] == (N // 2 if swiglu else N) and M <= 64, "gemm_skinny: shapes")
+    _need(K == K2 and out.shape[0] >= M and out.shape[1] == (N // 2 if swiglu else N) and M <= SKINNY_MAX_ROWS, "gemm_skinny: shapes")
     _need(_tc_ok(a, w, out), "gemm_skinny: operands must be bfloat16 with 16-byte aligned rows")
     _need(not swiglu or (N % 128 == 0 and out.dtype == torch.bfloat16), "gemm_skinny: swiglu needs N % 128 == 0 and bf16 out")
     splits = 1 if swiglu else (skinny_splits(N, K, M) if splits is None else splits)
@@ -513,7 +537,7 @@ def matmul(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
     always take the plain 32-bit kernel; bfloat16 operands take the tensor-core kernels when
     their rows are 16-byte aligned (few tokens: weights as tile rows), else the plain kernel."""
     if a.dtype == torch.bfloat16 and _tc_ok(a, w, out):
-        if a.shape[0] <= 64:
+        if weights_as_rows(a.shape[0], w.shape[0]):
             gemm_skinny(a, w, out)
         else:
             gemm_tcgen05(a, w, out)
@@ -604,7 +628,7 @@ def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
 
 def matmul_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) -> None:
     """out[M, I] = silu(a @ gate^T) * (a @ up^T) in one kernel; ``w_gate_up`` from ``interleave_gate_up``."""
-    if a.shape[0] <= 64:
+    if weights_as_rows(a.shape[0], w_gate_up.shape[0], swiglu=True):
         gemm_skinny(a, w_gate_up, out, swiglu=True)
     else:
         gemm_tcgen05(a, w_gate_up, out, swiglu=True)

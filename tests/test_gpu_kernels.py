@@ -373,7 +373,10 @@ def test_gemm_tcgen05(ops, out_dtype, M, N, K):
 
 @pytest.mark.parametrize("out_dtype", ["bfloat16", "float32"])
 @pytest.mark.parametrize("M,N,K,splits", [(1, 128, 64, 1), (8, 4096, 4096, None), (16, 1000, 520, 3), (17, 130, 1024, 4),
-                                          (33, 257, 72, 2), (64, 6144, 4096, None), (5, 1003, 14336, None), (3, 200, 64, 1)])
+                                          (33, 257, 72, 2), (64, 6144, 4096, None), (5, 1003, 14336, None), (3, 200, 64, 1),
+                                          # more than 64 tokens: several tiles of 64 tokens per weight tile
+                                          (65, 300, 264, 1), (96, 4096, 4096, None), (128, 1000, 520, 3), (200, 130, 1024, 4),
+                                          (256, 6144, 2048, None), (129, 257, 72, 1), (300, 1000, 520, 2), (512, 4096, 4096, None)])
 def test_gemm_skinny(ops, out_dtype, M, N, K, splits):
     torch.manual_seed(11)
     a = torch.randn(M, K, device=DEV).bfloat16()
@@ -602,6 +605,7 @@ def test_the_windows_edge_is_exact(ops, kernel, window, n):
 
 
 @pytest.mark.parametrize("M,I,K", [(1, 64, 64), (8, 512, 192), (33, 14336 // 8, 4096 // 8), (64, 128, 72), (65, 512, 192),
+                                   (96, 1792, 520), (128, 256, 4096), (200, 448, 136), (256, 2560, 2048), (257, 512, 192),
                                    (300, 1792, 520), (2048, 256, 4096), (2048, 2560, 2048), (1100, 1792, 520)])
 def test_gate_up_product_with_swiglu_epilogue(ops, M, I, K):
     torch.manual_seed(18)
