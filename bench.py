@@ -17,7 +17,7 @@ prompt, context limit 4096).  One JSON line is printed:
                 its time over the bf16 peak;
 * ``roofline``  for the decode step: the bytes it has to read (every weight once, and the
                 keys and values of the live sequences) over its time, against the HBM peak;
-* ``points``    decode tokens a second at batch 1 and 64 with their roofline fractions, and the
+* ``points``    decode tokens a second at batch 1, 64 and 128 with their roofline fractions, and the
                 rates of the two other workloads; ``workloads`` has their sizes, bytes and flops,
                 and their decode rates with CUDA graphs on and off;
 * ``checks``    what was verified beside the clock: after every timed region the device's report
@@ -361,7 +361,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--no-points", action="store_true",
-                    help="only the headline: skip the prefill, the batch 1 and 64 points and the two other workloads")
+                    help="only the headline: skip the prefill, the batch 1, 64 and 128 points and the two other workloads")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -378,7 +378,7 @@ def main():
     cfg = dict(LLAMA31_8B, num_hidden_layers=args.layers)
     pk = peaks()
     checks = {}
-    max_batch = max(args.batch, 1 if args.no_points else 64)
+    max_batch = max(args.batch, 1 if args.no_points else 128)
     model = kl.random_model(config_from_dict(cfg), seed=0, dtype=args.dtype, device="cuda:0")
     infer = kl.Inference(model, max_tokens=max_batch * CONTEXT, max_batch=max_batch, max_seq_len=CONTEXT)
     esize = 2 if args.dtype == "bfloat16" else 4
@@ -397,7 +397,7 @@ def main():
     d2h = args.batch * 4                                                          # the sampled token ids
 
     line = {
-        "metric": "decode tok/s, Llama-3.1-8B shape bf16, batch 8 (also batch 1/64 and prefill tok/s at 2048 tokens)",
+        "metric": "decode tok/s, Llama-3.1-8B shape bf16, batch 8 (also batch 1/64/128 and prefill tok/s at 2048 tokens)",
         "value": round(value, 2), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16" if args.dtype == "bfloat16" else "fp32", "data": "synthetic: random weights N(0, 0.02), uniform random token ids",
@@ -426,7 +426,7 @@ def main():
                            "frac_of_sustained": round(flops / t / (pk["bf16_tflops_sustained"] * 1e12), 4),
                            "tflop": round(flops / 1e12, 3)}
         points = {}
-        for b in (1, 64):
+        for b in (1, 64, 128):        # 128 sequences: beyond the 64-token tiles of the decode products
             k = max(16, args.steps // 2)
             s, ctx, _ = time_decode(infer, b, k, args.warmup, seed=3 + b, checks=checks)
             byts, _, _ = decode_bytes(cfg, args.layers, b * ctx, esize)
