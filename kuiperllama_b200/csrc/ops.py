@@ -75,7 +75,14 @@ def _ptr(t: Optional[torch.Tensor]) -> ctypes.c_void_p:
     return ctypes.c_void_p(0 if t is None else t.data_ptr())
 
 
+# The current stream's handle, once per launch: torch.cuda.current_stream() builds a Stream object and
+# looks the device up three times (7 us); the raw call behind it takes a fraction of a microsecond.
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream() -> ctypes.c_void_p:
+    if _raw_stream is not None:
+        return ctypes.c_void_p(_raw_stream(torch.cuda.current_device()))
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
@@ -302,6 +309,11 @@ def status_word(device: torch.device) -> torch.Tensor:
     return device_words(device)[0:1]
 
 
+def _status_ptr(device: torch.device) -> ctypes.c_void_p:
+    """The status word's address (word 0 of ``device_words``) for a launch, without a tensor view."""
+    return ctypes.c_void_p(device_words(device).data_ptr())
+
+
 def error_word(device: torch.device) -> torch.Tensor:
     return device_words(device)[1:2]
 
@@ -334,14 +346,15 @@ def check_status(device: torch.device) -> None:
         raise KernelError(f"a tensor-core kernel gave up waiting (code {code}: 1 = loader, 2 = MMA issuer, 3 = epilogue)")
 
 
-def _tc_ok(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
+def _tc_ok(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor]) -> bool:
     """Whether the TMA-fed tensor-core kernels take these operands: bfloat16, rows that start
-    on 16-byte boundaries (K and the row strides multiples of 8 elements)."""
+    on 16-byte boundaries (K and the row strides multiples of 8 elements).  ``out`` None: the
+    kernel's own float32 pieces."""
     K = a.shape[1]
-    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and out.dtype in (torch.bfloat16, torch.float32)
+    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+            and (out is None or (out.dtype in (torch.bfloat16, torch.float32) and out.stride(1) == 1))
             and K % 8 == 0 and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
-            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and a.stride(1) == 1 and w.stride(1) == 1
-            and out.stride(1) == 1)
+            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and a.stride(1) == 1 and w.stride(1) == 1)
 
 
 _sm_counts: Dict[int, int] = {}
@@ -381,7 +394,7 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bo
     _check(lib("gemm_tcgen05").kl_gemm_tcgen05(_ptr(a), ctypes.c_longlong(a.stride(0)), _ptr(w),
                                                ctypes.c_longlong(w.stride(0)), _ptr(out), ctypes.c_longlong(out.stride(0)),
                                                M, N, K, int(out.dtype == torch.float32), int(swiglu),
-                                               _ptr(status_word(a.device)), _stream()), "gemm_tcgen05")
+                                               _status_ptr(a.device), _stream()), "gemm_tcgen05")
 
 
 # arguments of kl_gemm_tcgen05_skinny that switch the residual-stream forms off
@@ -426,7 +439,7 @@ def gemm_skinny_stream(w: torch.Tensor, a: torch.Tensor, row_scale=None, sink=No
         scale_args = (ctypes.c_void_p(0), 0, ctypes.c_float(0.0))
     dev = w.device
     L = lib("gemm_tcgen05")
-    st = _ptr(status_word(dev))
+    st = _status_ptr(dev)
     null = ctypes.c_void_p(0)
     if swiglu:
         _need(sink is None and N % 128 == 0, "gemm_skinny_stream: swiglu")
@@ -490,8 +503,7 @@ def gemm_skinny_partials(a: torch.Tensor, w: torch.Tensor, splits: Optional[int]
     (M, K), (N, K2) = a.shape, w.shape
     if not weights_as_rows(M, N) or a.dtype != torch.bfloat16 or K != K2:
         return None
-    probe = torch.empty((0, N), dtype=torch.float32, device=a.device)
-    if not _tc_ok(a, w, probe):
+    if not _tc_ok(a, w, None):
         return None
     splits = skinny_splits(N, K, M) if splits is None else splits
     if splits <= 1:
@@ -499,7 +511,7 @@ def gemm_skinny_partials(a: torch.Tensor, w: torch.Tensor, splits: Optional[int]
     partial = torch.empty((splits, M, N), dtype=torch.float32, device=a.device)
     _check(lib("gemm_tcgen05").kl_gemm_tcgen05_skinny(
         _ptr(a), ctypes.c_longlong(a.stride(0)), _ptr(w), ctypes.c_longlong(w.stride(0)), _ptr(partial),
-        ctypes.c_longlong(N), M, N, K, splits, 1, 0, *_NO_STREAM_FUSION, _ptr(status_word(a.device)), _stream()),
+        ctypes.c_longlong(N), M, N, K, splits, 1, 0, *_NO_STREAM_FUSION, _status_ptr(a.device), _stream()),
         "gemm_skinny")
     return partial
 
@@ -517,7 +529,7 @@ def gemm_skinny(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, splits: Opt
     _need(not swiglu or (N % 128 == 0 and out.dtype == torch.bfloat16), "gemm_skinny: swiglu needs N % 128 == 0 and bf16 out")
     splits = 1 if swiglu else (skinny_splits(N, K, M) if splits is None else splits)
     L = lib("gemm_tcgen05")
-    st = _ptr(status_word(a.device))
+    st = _status_ptr(a.device)
     if splits == 1:
         _check(L.kl_gemm_tcgen05_skinny(_ptr(a), ctypes.c_longlong(a.stride(0)), _ptr(w), ctypes.c_longlong(w.stride(0)),
                                         _ptr(out), ctypes.c_longlong(out.stride(0)), M, N, K, 1,
@@ -653,7 +665,7 @@ def attention_tcgen05(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache
     _check(lib("attention_tcgen05").kl_attention_tcgen05(
         _ptr(q), q_stride, _ptr(out), _ptr(k_cache), _ptr(v_cache), ctypes.c_longlong(cache_rows), _ptr(block_table),
         block_table.shape[1], _ptr(cu_tokens), _ptr(seq_slots), _ptr(seq_starts), _ptr(seq_new), n_seqs, max_new,
-        q.shape[0], num_heads, num_kv_heads, head_dim, ctypes.c_float(scale), _ptr(status_word(q.device)), _stream()),
+        q.shape[0], num_heads, num_kv_heads, head_dim, ctypes.c_float(scale), _status_ptr(q.device), _stream()),
         "attention_tcgen05")
 
 
