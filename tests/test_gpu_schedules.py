@@ -4,9 +4,9 @@ implementation in float32 and bfloat16, for a head size of 64 (tiny3) and of 128
 * a prompt fed in several multi-token steps that cross page borders (a sequence that already
   holds tokens brings more than one: both tensor-core prefill kernels with ``seq_starts > 0``);
 * a mixed step in which a fresh prompt joins sequences that are decoding;
-* decode steps replayed from CUDA graphs at 8, 20, 33 and 64 sequences (the 16-, 32- and
-  64-token tiles of the weights-as-rows products; decode attention with several pieces and with
-  one piece per sequence; its three-stage form at 64 sequences of 8 kv heads);
+* decode steps replayed from CUDA graphs at 8, 20, 33, 64, 96 and 130 sequences (the 16-, 32-, 64- and
+  128-token tiles of the weights-as-rows products; decode attention with several pieces and with
+  one piece per sequence; its light CTAs from 64 sequences of 8 kv heads on);
 * the option that folds the norms into the products at 3 and 4 sequences.
 
 The models here have weights N(0, 0.08), see ``SHARP``.
@@ -120,11 +120,12 @@ def test_a_fresh_prompt_joins_decoding_sequences(models, name, dtype):
     engine.check_device_errors()
 
 
-@pytest.mark.parametrize("batch", [8, 20, 33, 64])
+@pytest.mark.parametrize("batch", [8, 20, 33, 64, 96, 130])
 @pytest.mark.parametrize("name", CONFIGS)
 def test_graph_decode_at_larger_batches(models, name, batch):
-    """bfloat16 decode steps replayed from a CUDA graph at batch sizes that take the 16-, 32- and
-    64-token tiles of the products and every form of the decode attention; the same steps
+    """bfloat16 decode steps replayed from a CUDA graph at batch sizes that take the 16-, 32-, 64- and
+    128-token tiles of the products (130: two tiles of tokens per weight tile) and every form of the
+    decode attention; the same steps
     without a graph give the same bits, and both agree with the plain implementation."""
     from kuiperllama_b200.engine import SequenceInput
     model, folder = models(name, "bfloat16")
