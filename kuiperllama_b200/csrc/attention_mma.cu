@@ -102,6 +102,120 @@ struct DecodeFuse {
     int* counters;                // [rows * KV], zero
 };
 
+// The decode step's token of one sequence, for one kv group: its q (the group's G heads) into q_sm
+// [G][HD], and with `writes_token` its k and v into the cache at element offset `dst`.  The values are
+// the sum of the q/k/v product's float32 pieces (or the bfloat16 qkv row), q and k rotated by the angles
+// whose cos and sin are in rot_cs / rot_sn [HD / 2] (k by `k_position` itself where it differs from q's).
+// Work is cut into items of four neighbouring elements (and their four rotation partners), one per
+// thread and turn, and an item's loads are all requested before any is used: the CTA waits for
+// memory once.
+template <int HD, int THREADS>
+__device__ __forceinline__ void make_token_qkv(const DecodeFuse& fuse, bf16* q_sm, const float* rot_cs, const float* rot_sn,
+                                               int G, int H, int KV, int g, size_t q_row, size_t kv_row, bool writes_token,
+                                               size_t dst, bool k_at_q_position, int k_position) {
+    const int width = (H + 2 * KV) * HD;
+    constexpr int QI = HD / 8;                       // items per head: HD / 2 pairs, four at a time
+    const int n_q = G * QI, n_k = writes_token ? QI : 0, n_v = writes_token ? HD / 4 : 0;
+    // A CTA of fewer than 128 threads takes two items per thread and turn (and four pieces at a time
+    // instead of eight), so that it still waits for memory once.
+    constexpr int IT = THREADS >= 128 ? 1 : 2, PC = 8 / IT;
+    const int n_items = n_q + n_k + n_v;
+    for (int base = 0; base < n_items; base += IT * THREADS) {
+        bool live[IT], is_q[IT], is_k[IT], rot[IT];
+        int hh[IT], j[IT];
+        size_t off[IT];
+        float4 x[IT], y[IT];
+#pragma unroll
+        for (int e = 0; e < IT; ++e) {
+            const int item = base + e * THREADS + threadIdx.x;
+            live[e] = item < n_items;
+            is_q[e] = item < n_q;
+            is_k[e] = !is_q[e] && item < n_q + n_k;
+            hh[e] = is_q[e] ? item / QI : 0;
+            j[e] = is_q[e] ? (item % QI) * 4 : (is_k[e] ? (item - n_q) * 4 : (item - n_q - n_k) * 4);
+            const int col = is_q[e] ? (g * G + hh[e]) * HD + j[e] : (is_k[e] ? (H + g) * HD + j[e] : (H + KV + g) * HD + j[e]);
+            off[e] = (is_q[e] ? q_row : kv_row) * width + col;
+            rot[e] = is_q[e] || is_k[e];
+            x[e] = y[e] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        if (fuse.n_partials == 0) {
+#pragma unroll
+            for (int e = 0; e < IT; ++e) {
+                if (!live[e]) continue;
+                const uint2 rx = *reinterpret_cast<const uint2*>(fuse.qkv + off[e]);
+                const float2 x01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&rx.x));
+                const float2 x23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&rx.y));
+                x[e] = make_float4(x01.x, x01.y, x23.x, x23.y);
+                if (rot[e]) {
+                    const uint2 ry = *reinterpret_cast<const uint2*>(fuse.qkv + off[e] + HD / 2);
+                    const float2 y01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ry.x));
+                    const float2 y23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ry.y));
+                    y[e] = make_float4(y01.x, y01.y, y23.x, y23.y);
+                }
+            }
+        } else {
+            for (int z0 = 0; z0 < fuse.n_partials; z0 += PC) {     // pieces are added in ascending order
+                float4 px[IT][PC], py[IT][PC];
+#pragma unroll
+                for (int e = 0; e < IT; ++e) {
+#pragma unroll
+                    for (int zz = 0; zz < PC; ++zz) {
+                        const float* p = fuse.partials + (size_t)(z0 + zz) * fuse.partial_stride + off[e];
+                        const bool in = live[e] && z0 + zz < fuse.n_partials;
+                        px[e][zz] = in ? __ldcg(reinterpret_cast<const float4*>(p)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                        py[e][zz] = (in && rot[e]) ? __ldcg(reinterpret_cast<const float4*>(p + HD / 2)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
+                }
+#pragma unroll
+                for (int e = 0; e < IT; ++e) {
+#pragma unroll
+                    for (int zz = 0; zz < PC; ++zz) {
+                        x[e].x += px[e][zz].x; x[e].y += px[e][zz].y; x[e].z += px[e][zz].z; x[e].w += px[e][zz].w;
+                        y[e].x += py[e][zz].x; y[e].y += py[e][zz].y; y[e].z += py[e][zz].z; y[e].w += py[e][zz].w;
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < IT; ++e) {
+            if (!live[e]) continue;
+            uint2 lo_half, hi_half;                  // elements j..j+3 and their partners j + HD / 2 ..
+            if (rot[e]) {
+                float sn[4], cs[4];
+                if (is_q[e] || k_at_q_position) {            // a decode step's one token: q and k share the position
+                    const float4 c4 = *reinterpret_cast<const float4*>(rot_cs + j[e]), s4 = *reinterpret_cast<const float4*>(rot_sn + j[e]);
+                    cs[0] = c4.x; cs[1] = c4.y; cs[2] = c4.z; cs[3] = c4.w;
+                    sn[0] = s4.x; sn[1] = s4.y; sn[2] = s4.z; sn[3] = s4.w;
+                } else {
+                    const float4 f = *reinterpret_cast<const float4*>(fuse.inv_freq + j[e]);
+                    const float angle = (float)k_position;
+                    sincosf(angle * f.x, &sn[0], &cs[0]);
+                    sincosf(angle * f.y, &sn[1], &cs[1]);
+                    sincosf(angle * f.z, &sn[2], &cs[2]);
+                    sincosf(angle * f.w, &sn[3], &cs[3]);
+                }
+                lo_half.x = pack_bf16(x[e].x * cs[0] - y[e].x * sn[0], x[e].y * cs[1] - y[e].y * sn[1]);
+                lo_half.y = pack_bf16(x[e].z * cs[2] - y[e].z * sn[2], x[e].w * cs[3] - y[e].w * sn[3]);
+                hi_half.x = pack_bf16(y[e].x * cs[0] + x[e].x * sn[0], y[e].y * cs[1] + x[e].y * sn[1]);
+                hi_half.y = pack_bf16(y[e].z * cs[2] + x[e].z * sn[2], y[e].w * cs[3] + x[e].w * sn[3]);
+            } else {
+                lo_half.x = pack_bf16(x[e].x, x[e].y);
+                lo_half.y = pack_bf16(x[e].z, x[e].w);
+                hi_half = lo_half;
+            }
+            if (is_q[e]) {
+                *reinterpret_cast<uint2*>(q_sm + hh[e] * HD + j[e]) = lo_half;
+                *reinterpret_cast<uint2*>(q_sm + hh[e] * HD + j[e] + HD / 2) = hi_half;
+            } else if (is_k[e]) {
+                *reinterpret_cast<uint2*>(fuse.k_cache_w + dst + j[e]) = lo_half;
+                *reinterpret_cast<uint2*>(fuse.k_cache_w + dst + j[e] + HD / 2) = hi_half;
+            } else {
+                *reinterpret_cast<uint2*>(fuse.v_cache_w + dst + j[e]) = lo_half;
+            }
+        }
+    }
+}
+
 // SK: keys per stage, a cache page (64) or half of one.  Half pages with two warps make a CTA of the
 // decode layout light enough (48 KB of stages at a head size of 128) for four of them on an SM.
 template <int HD, int WM, int WN, int NS, int SK>
@@ -194,114 +308,13 @@ attention_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict_
     }
     // query fragments
     uint32_t qa[KS][4];
-    const int width = (H + 2 * KV) * HD;
     if (fuse.enabled) {
         // The token's q (this group's heads), and in the CTA whose pages end at the token also its k
-        // and v, are made here: the sum of the product's pieces, rotated.  Work is cut into items of
-        // four neighbouring elements (and their four rotation partners), one per thread and turn, and
-        // an item's loads are all requested before any is used: the CTA waits for memory once.
+        // and v, are made here: the sum of the product's pieces, rotated.
         __shared__ __align__(16) bf16 q_sm[16 * HD];
-        constexpr int QI = HD / 8;                       // items per head: HD / 2 pairs, four at a time
-        const int n_q = G * QI, n_k = writes_token ? QI : 0, n_v = writes_token ? HD / 4 : 0;
         const size_t dst = writes_token ? (((size_t)table[max_pos / PAGE] * KV + g) * PAGE + (max_pos % PAGE)) * HD : 0;
-        // A CTA of fewer than 128 threads takes two items per thread and turn (and four pieces at a time
-        // instead of eight), so that it still waits for memory once.
-        constexpr int IT = THREADS >= 128 ? 1 : 2, PC = 8 / IT;
-        const int n_items = n_q + n_k + n_v;
-        for (int base = 0; base < n_items; base += IT * THREADS) {
-            bool live[IT], is_q[IT], is_k[IT], rot[IT];
-            int hh[IT], j[IT];
-            size_t off[IT];
-            float4 x[IT], y[IT];
-#pragma unroll
-            for (int e = 0; e < IT; ++e) {
-                const int item = base + e * THREADS + threadIdx.x;
-                live[e] = item < n_items;
-                is_q[e] = item < n_q;
-                is_k[e] = !is_q[e] && item < n_q + n_k;
-                hh[e] = is_q[e] ? item / QI : 0;
-                j[e] = is_q[e] ? (item % QI) * 4 : (is_k[e] ? (item - n_q) * 4 : (item - n_q - n_k) * 4);
-                const int col = is_q[e] ? (g * G + hh[e]) * HD + j[e] : (is_k[e] ? (H + g) * HD + j[e] : (H + KV + g) * HD + j[e]);
-                off[e] = (size_t)(is_q[e] ? row0 + t0 : row0) * width + col;
-                rot[e] = is_q[e] || is_k[e];
-                x[e] = y[e] = make_float4(0.f, 0.f, 0.f, 0.f);
-            }
-            if (fuse.n_partials == 0) {
-#pragma unroll
-                for (int e = 0; e < IT; ++e) {
-                    if (!live[e]) continue;
-                    const uint2 rx = *reinterpret_cast<const uint2*>(fuse.qkv + off[e]);
-                    const float2 x01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&rx.x));
-                    const float2 x23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&rx.y));
-                    x[e] = make_float4(x01.x, x01.y, x23.x, x23.y);
-                    if (rot[e]) {
-                        const uint2 ry = *reinterpret_cast<const uint2*>(fuse.qkv + off[e] + HD / 2);
-                        const float2 y01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ry.x));
-                        const float2 y23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ry.y));
-                        y[e] = make_float4(y01.x, y01.y, y23.x, y23.y);
-                    }
-                }
-            } else {
-                for (int z0 = 0; z0 < fuse.n_partials; z0 += PC) {     // pieces are added in ascending order
-                    float4 px[IT][PC], py[IT][PC];
-#pragma unroll
-                    for (int e = 0; e < IT; ++e) {
-#pragma unroll
-                        for (int zz = 0; zz < PC; ++zz) {
-                            const float* p = fuse.partials + (size_t)(z0 + zz) * fuse.partial_stride + off[e];
-                            const bool in = live[e] && z0 + zz < fuse.n_partials;
-                            px[e][zz] = in ? __ldcg(reinterpret_cast<const float4*>(p)) : make_float4(0.f, 0.f, 0.f, 0.f);
-                            py[e][zz] = (in && rot[e]) ? __ldcg(reinterpret_cast<const float4*>(p + HD / 2)) : make_float4(0.f, 0.f, 0.f, 0.f);
-                        }
-                    }
-#pragma unroll
-                    for (int e = 0; e < IT; ++e) {
-#pragma unroll
-                        for (int zz = 0; zz < PC; ++zz) {
-                            x[e].x += px[e][zz].x; x[e].y += px[e][zz].y; x[e].z += px[e][zz].z; x[e].w += px[e][zz].w;
-                            y[e].x += py[e][zz].x; y[e].y += py[e][zz].y; y[e].z += py[e][zz].z; y[e].w += py[e][zz].w;
-                        }
-                    }
-                }
-            }
-#pragma unroll
-            for (int e = 0; e < IT; ++e) {
-                if (!live[e]) continue;
-                uint2 lo_half, hi_half;                  // elements j..j+3 and their partners j + HD / 2 ..
-                if (rot[e]) {
-                    float sn[4], cs[4];
-                    if (is_q[e] || max_pos == start + t0) {      // a decode step's one token: q and k share the position
-                        const float4 c4 = *reinterpret_cast<const float4*>(rot_cs + j[e]), s4 = *reinterpret_cast<const float4*>(rot_sn + j[e]);
-                        cs[0] = c4.x; cs[1] = c4.y; cs[2] = c4.z; cs[3] = c4.w;
-                        sn[0] = s4.x; sn[1] = s4.y; sn[2] = s4.z; sn[3] = s4.w;
-                    } else {
-                        const float4 f = *reinterpret_cast<const float4*>(fuse.inv_freq + j[e]);
-                        const float angle = (float)max_pos;
-                        sincosf(angle * f.x, &sn[0], &cs[0]);
-                        sincosf(angle * f.y, &sn[1], &cs[1]);
-                        sincosf(angle * f.z, &sn[2], &cs[2]);
-                        sincosf(angle * f.w, &sn[3], &cs[3]);
-                    }
-                    lo_half.x = pack_bf16(x[e].x * cs[0] - y[e].x * sn[0], x[e].y * cs[1] - y[e].y * sn[1]);
-                    lo_half.y = pack_bf16(x[e].z * cs[2] - y[e].z * sn[2], x[e].w * cs[3] - y[e].w * sn[3]);
-                    hi_half.x = pack_bf16(y[e].x * cs[0] + x[e].x * sn[0], y[e].y * cs[1] + x[e].y * sn[1]);
-                    hi_half.y = pack_bf16(y[e].z * cs[2] + x[e].z * sn[2], y[e].w * cs[3] + x[e].w * sn[3]);
-                } else {
-                    lo_half.x = pack_bf16(x[e].x, x[e].y);
-                    lo_half.y = pack_bf16(x[e].z, x[e].w);
-                    hi_half = lo_half;
-                }
-                if (is_q[e]) {
-                    *reinterpret_cast<uint2*>(q_sm + hh[e] * HD + j[e]) = lo_half;
-                    *reinterpret_cast<uint2*>(q_sm + hh[e] * HD + j[e] + HD / 2) = hi_half;
-                } else if (is_k[e]) {
-                    *reinterpret_cast<uint2*>(fuse.k_cache_w + dst + j[e]) = lo_half;
-                    *reinterpret_cast<uint2*>(fuse.k_cache_w + dst + j[e] + HD / 2) = hi_half;
-                } else {
-                    *reinterpret_cast<uint2*>(fuse.v_cache_w + dst + j[e]) = lo_half;
-                }
-            }
-        }
+        make_token_qkv<HD, THREADS>(fuse, q_sm, rot_cs, rot_sn, G, H, KV, g, (size_t)(row0 + t0), (size_t)row0, writes_token, dst,
+                                    max_pos == start + t0, max_pos);
         __syncthreads();                                 // q_sm is whole; the CTA's own copies below read the new cache rows
 #pragma unroll
         for (int ks = 0; ks < KS; ++ks) {
@@ -393,7 +406,6 @@ attention_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict_
                 m[i] = m_new;
                 l[i] *= corr[i];
             }
-#pragma unroll
             if (__any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f)) {      // most blocks after the first leave the maxima alone
 #pragma unroll
                 for (int n = 0; n < ON; ++n) { o[n][0] *= corr[0]; o[n][1] *= corr[0]; o[n][2] *= corr[1]; o[n][3] *= corr[1]; }
