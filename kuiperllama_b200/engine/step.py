@@ -98,6 +98,14 @@ class Engine:
     # A captured step keeps its own activations and logits (64 sequences of a 128k vocabulary: 33 MB);
     # beyond this many the one replayed longest ago is dropped and captured again if it comes back.
     MAX_GRAPHS = 48
+    # Small steps that are not decode steps (a short prompt, a chunk of one) are captured too, since the
+    # host needs longer to launch their kernels one by one than the device to run them (8B shape, 128
+    # tokens: 161 us of host time per layer, about 110 us of kernels).  Their rows are padded to a
+    # multiple of 64, and a captured step serves every step of as many sequences, padded rows and
+    # wanted places.
+    SMALL_STEP_TOKENS = 512
+    SMALL_STEP_SEQS = 8
+    MAX_STEP_GRAPHS = 16
 
     def __init__(self, model: DecoderModel, cache: SequenceCache, use_graphs: bool = False):
         self.model = model
@@ -106,6 +114,7 @@ class Engine:
         self.use_graphs = use_graphs
         self._staging: Optional[_Staging] = None
         self._graphs: Dict[Tuple[int, int], _DecodeGraph] = {}        # (sequences, context class) -> captured step
+        self._step_graphs: Dict[Tuple[int, int, int], _DecodeGraph] = {}   # (sequences, padded rows, wanted places) -> captured small step
 
     # ------------------------------------------------------------------ slots
     def alloc_slot(self) -> int:
@@ -189,6 +198,8 @@ class Engine:
         """Run one step.  Returns float32 logits [wanted, vocab] in the order of ``inputs``
         and of each ``want`` (None when nothing is wanted).  ``pad_rows`` appends rows that
         belong to no sequence; they change no result."""
+        if self.use_graphs and pad_rows == 0 and self._is_small_step(inputs):
+            return self._small_step(inputs)
         ctx, want_rows, n_want = self._pack(inputs, pad_rows)
         residual, pending = self.model.hidden_states(ctx, self.cache)
         for s, st, n in zip(inputs, ctx.host_starts, ctx.host_new):
@@ -196,6 +207,52 @@ class Engine:
         if n_want == 0:
             return None
         return self.model.logits(residual, pending, want_rows)
+
+    def _is_small_step(self, inputs: Sequence[SequenceInput]) -> bool:
+        if not 1 <= len(inputs) <= self.SMALL_STEP_SEQS:
+            return False
+        n = sum(len(s.tokens) for s in inputs)
+        return n <= self.SMALL_STEP_TOKENS and any(len(s.tokens) > 1 for s in inputs)
+
+    def _small_step(self, inputs: Sequence[SequenceInput]) -> Optional[torch.Tensor]:
+        """A small step through a CUDA graph: the rows padded to a multiple of 64, the attention's
+        grid sized for sequences of up to that many new tokens, everything else read from the staging
+        buffer and the block tables as in any step.  The first step of a key runs kernel by kernel
+        and is then captured.  The logits are a copy (the graph's own buffer is written by the next
+        replay)."""
+        from ..csrc import ops
+        n_real = sum(len(s.tokens) for s in inputs)
+        rows = -(-n_real // PAGE) * PAGE
+        ctx, want_rows, n_want = self._pack(inputs, rows - n_real)
+        ctx.max_new = rows                                # every length a replay may bring
+        key = (ctx.n_seqs, rows, n_want)
+        g = self._step_graphs.get(key)
+        if g is not None and g.staging_ptr != self._staging.dev.data_ptr():
+            self._step_graphs.clear()                     # the staging buffer moved: captured addresses are stale
+            self._graphs.clear()
+            g = None
+        if g is None:
+            residual, pending = self.model.hidden_states(ctx, self.cache)
+            logits = self.model.logits(residual, pending, want_rows) if n_want else None
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            before = ops.launch_count
+            with torch.cuda.graph(graph):
+                r2, p2 = self.model.hidden_states(ctx, self.cache)
+                static_logits = self.model.logits(r2, p2, want_rows) if n_want else None
+            captured = ops.launch_count - before
+            ops.launch_count = before
+            self._step_graphs[key] = _DecodeGraph(graph, static_logits, self._staging.dev.data_ptr(), captured)
+            while len(self._step_graphs) > self.MAX_STEP_GRAPHS:
+                self._step_graphs.pop(next(iter(self._step_graphs)))
+        else:
+            self._step_graphs[key] = self._step_graphs.pop(key)      # most recently used last
+            g.graph.replay()
+            ops.launch_count += g.launches
+            logits = g.logits.clone() if n_want else None
+        for s, st, n in zip(inputs, ctx.host_starts, ctx.host_new):
+            self.cache.lengths[s.slot] = st + n
+        return logits
 
     def decode_step(self, slots: Sequence[int], tokens) -> torch.Tensor:
         """One token for each of the given sequences; logits [len(slots), vocab].  ``tokens`` are
@@ -229,6 +286,7 @@ class Engine:
         ctx, want_rows, _ = self._pack(inputs, 0)
         if g is not None:                                 # the staging buffer moved: captured addresses are stale
             self._graphs.clear()
+            self._step_graphs.clear()
             g = None
         if g is None:
             # The first step of this size runs eagerly (it also warms every kernel up); then the

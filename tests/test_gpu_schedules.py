@@ -184,6 +184,48 @@ def test_graph_decode_crosses_a_context_class(model_folders, name):
             assert_close(outs[use_graphs][i], ref, "bfloat16", f"{name} across the class border, graphs {use_graphs}, request {i}", **WIDE)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", CONFIGS)
+def test_small_steps_replayed_from_cuda_graphs(models, name, dtype):
+    """Short prompts and chunks of prompts are captured too (rows padded to a multiple of 64).  Steps
+    that share a key (sequences, padded rows, wanted places) but differ in lengths, start positions
+    and slots replay one graph; their logits agree with the plain implementation and, in float32, are
+    the bits of the same steps launched kernel by kernel without padding."""
+    from kuiperllama_b200.engine import SequenceInput
+    model, folder = models(name, dtype)
+    vocab = config_dict(name)["vocab_size"]
+    reqs = [random_tokens(n, vocab, seed=2600 + n) for n in (150, 97, 120, 33, 61)]
+    ref = [plain_logits(folder, r) for r in reqs]
+    # (request, tokens it brings) per step; wanted: the last place of every sequence of the step
+    schedule = [[(0, 100)], [(1, 97)], [(0, 50), (2, 60)], [(2, 60), (3, 33)], [(4, 40)], [(4, 21)]]
+    outs = {}
+    for use_graphs in (False, True):
+        engine = _engine(model, 64 * 16, use_graphs=use_graphs)
+        done = [0] * len(reqs)
+        slots = {}
+        got = []
+        with torch.inference_mode():
+            for step in schedule:
+                inputs = []
+                for i, n in step:
+                    if i not in slots:
+                        slots[i] = engine.alloc_slot()
+                    inputs.append(SequenceInput(slots[i], reqs[i][done[i]:done[i] + n], [n - 1]))
+                logits = engine.step(inputs)
+                for j, (i, n) in enumerate(step):
+                    done[i] += n
+                    got.append((i, done[i] - 1, logits[j].clone()))
+        if use_graphs:
+            # (1 sequence, 128 rows), (1, 64) used three times, (2, 128) used twice
+            assert sorted(engine._step_graphs) == [(1, 64, 1), (1, 128, 1), (2, 128, 2)]
+        engine.check_device_errors()
+        outs[use_graphs] = got
+    for (i, place, a), (_, _, b) in zip(outs[True], outs[False]):
+        if dtype == "float32":       # (bfloat16: the padded rows change how the products cut their K range, so the last bits differ)
+            assert torch.equal(a, b), f"request {i} place {place}: a captured small step gave other logits than the step launched kernel by kernel"
+        assert_close(a[None], ref[i][place:place + 1], dtype, f"{name} small steps from graphs, request {i} place {place}", **WIDE)
+
+
 @pytest.mark.parametrize("n_seqs", [3, 4])
 @pytest.mark.parametrize("name", CONFIGS)
 def test_stream_fusion_at_three_and_four_sequences(models, model_folders, name, n_seqs):
