@@ -9,6 +9,8 @@ repeats, a buffer larger than L2 written between repeats), and print the achieve
     python microbench.py decode_step --shape 8b --layers 4 --batch 32 --context 8300 [--splits 2]
         (decode steps of a few layers of one of bench.py's shapes, replayed from a CUDA graph; --splits
         fixes the number of pieces the decode attention cuts a sequence into, else the package's rule)
+    python microbench.py prefill_step --shape 8b --layers 2 --tokens 2048
+        (one prompt through a few layers, launched kernel by kernel: the case for a launch list)
 
 It is also the small case that profiler captures of single kernels are taken on.
 """
@@ -94,9 +96,41 @@ def _decode_step(args) -> int:
     return 0
 
 
+def _prefill_step(args) -> int:
+    import bench
+    import kuiperllama_b200 as kl
+    from kuiperllama_b200.config import config_from_dict
+    from kuiperllama_b200.engine import Engine, SequenceInput
+    base = {"8b": bench.LLAMA31_8B, "7b": bench.LLAMA2_7B, "1b": bench.LLAMA32_1B}[args.shape]
+    T, L = args.tokens, args.layers
+    cfg = dict(base, num_hidden_layers=L, max_position_embeddings=max(base["max_position_embeddings"], T))
+    model = kl.random_model(config_from_dict(cfg), seed=0)
+    eng = Engine(model, model.new_cache(max_tokens=T + ops.PAGE, max_seq_len=T), use_graphs=False)
+    g = torch.Generator().manual_seed(1)
+    prompt = torch.randint(0, cfg["vocab_size"], (T,), generator=g).tolist()
+    times = []
+    with torch.inference_mode():
+        for _ in range(3 + args.repeats):
+            slot = eng.alloc_slot()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            eng.step([SequenceInput(slot, prompt, [T - 1])])
+            b.record()
+            torch.cuda.synchronize()
+            eng.free_slot(slot)
+            times.append(a.elapsed_time(b))
+    eng.check_device_errors()
+    times = sorted(times[3:])
+    ms = times[len(times) // 2]
+    print(json.dumps({"kernel": "prefill_step", "shape": args.shape, "layers": L, "tokens": T, "ms": round(ms, 3),
+                      "us_per_layer": round(ms * 1e3 / L, 1)}))
+    return 0
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="microbench")
-    ap.add_argument("kernel", choices=["gemm_skinny", "gemm_tcgen05", "attention_prefill", "attention_decode", "decode_step"])
+    ap.add_argument("kernel", choices=["gemm_skinny", "gemm_tcgen05", "attention_prefill", "attention_decode", "decode_step",
+                                           "prefill_step"])
     ap.add_argument("--shape", default="8b", choices=["8b", "7b", "1b"], help="decode_step: which of bench.py's shapes")
     ap.add_argument("--layers", type=int, default=4, help="decode_step: layers of the model")
     ap.add_argument("--steps", type=int, default=150, help="decode_step: timed steps")
@@ -121,6 +155,8 @@ def main(argv=None) -> int:
     out = {"kernel": args.kernel}
     if args.kernel == "decode_step":
         return _decode_step(args)
+    if args.kernel == "prefill_step":
+        return _prefill_step(args)
     if args.kernel in ("gemm_skinny", "gemm_tcgen05"):
         a = torch.randn(args.m, args.k, device=DEV).bfloat16()
         w = torch.randn(args.n, args.k, device=DEV).bfloat16()
