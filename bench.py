@@ -62,6 +62,14 @@ LLAMA32_1B = {
     "vocab_size": 128256, "max_position_embeddings": 4096, "rms_norm_eps": 1e-5, "rope_theta": 500000.0,
     "rope_scaling": dict(_LLAMA3_ROPE, factor=32.0), "tie_word_embeddings": True, "hidden_act": "silu",
 }
+# Not one of the bench's workloads: the largest Llama shape whose weights fit one B200 in bfloat16 (141 GB),
+# for `microbench.py decode_step / prefill_step --shape 70b` on a few of its layers.
+LLAMA3_70B = {
+    "architectures": ["LlamaForCausalLM"], "hidden_size": 8192, "intermediate_size": 28672,
+    "num_hidden_layers": 80, "num_attention_heads": 64, "num_key_value_heads": 8, "head_dim": 128,
+    "vocab_size": 128256, "max_position_embeddings": 8192, "rms_norm_eps": 1e-5, "rope_theta": 500000.0,
+    "rope_scaling": dict(_LLAMA3_ROPE, factor=8.0), "tie_word_embeddings": False, "hidden_act": "silu",
+}
 PROMPT_LEN = 512
 PREFILL_LEN = 2048
 CONTEXT = 4096

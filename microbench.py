@@ -64,7 +64,7 @@ def _decode_step(args) -> int:
     from kuiperllama_b200.config import config_from_dict
     from kuiperllama_b200.engine import Engine, SequenceInput
     from kuiperllama_b200.engine.step import context_class
-    base = {"8b": bench.LLAMA31_8B, "7b": bench.LLAMA2_7B, "1b": bench.LLAMA32_1B}[args.shape]
+    base = {"8b": bench.LLAMA31_8B, "7b": bench.LLAMA2_7B, "1b": bench.LLAMA32_1B, "70b": bench.LLAMA3_70B}[args.shape]
     B, N, L = args.batch, args.context, args.layers
     cfg = dict(base, num_hidden_layers=L, max_position_embeddings=max(base["max_position_embeddings"], N + args.steps + 16))
     model = kl.random_model(config_from_dict(cfg), seed=0)
@@ -101,7 +101,7 @@ def _prefill_step(args) -> int:
     import kuiperllama_b200 as kl
     from kuiperllama_b200.config import config_from_dict
     from kuiperllama_b200.engine import Engine, SequenceInput
-    base = {"8b": bench.LLAMA31_8B, "7b": bench.LLAMA2_7B, "1b": bench.LLAMA32_1B}[args.shape]
+    base = {"8b": bench.LLAMA31_8B, "7b": bench.LLAMA2_7B, "1b": bench.LLAMA32_1B, "70b": bench.LLAMA3_70B}[args.shape]
     T, L = args.tokens, args.layers
     cfg = dict(base, num_hidden_layers=L, max_position_embeddings=max(base["max_position_embeddings"], T))
     model = kl.random_model(config_from_dict(cfg), seed=0)
@@ -131,7 +131,7 @@ def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="microbench")
     ap.add_argument("kernel", choices=["gemm_skinny", "gemm_tcgen05", "attention_prefill", "attention_decode", "decode_step",
                                            "prefill_step"])
-    ap.add_argument("--shape", default="8b", choices=["8b", "7b", "1b"], help="decode_step: which of bench.py's shapes")
+    ap.add_argument("--shape", default="8b", choices=["8b", "7b", "1b", "70b"], help="decode_step: which of bench.py's shapes")
     ap.add_argument("--layers", type=int, default=4, help="decode_step: layers of the model")
     ap.add_argument("--steps", type=int, default=150, help="decode_step: timed steps")
     ap.add_argument("--m", type=int, default=8)
