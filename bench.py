@@ -17,7 +17,9 @@ prompt, context limit 4096).  One JSON line is printed:
                 its time over the bf16 peak;
 * ``roofline``  for the decode step: the bytes it has to read (every weight once, and the
                 keys and values of the live sequences) over its time, against the HBM peak;
-* ``points``    decode tokens a second at batch 1, 64 and 128 with their roofline fractions, and the
+* ``points``    decode tokens a second at batch 1, 64 and 128 with their roofline fractions, the
+                headline's batch again after 40 warm-up steps (``decode_b8_settled``: the SM clock
+                needs some 14 steps to recover from the prefill's time under the power cap), and the
                 rates of the two other workloads; ``workloads`` has their sizes, bytes and flops,
                 and their decode rates with CUDA graphs on and off;
 * ``checks``    what was verified beside the clock: after every timed region the device's report
@@ -434,6 +436,13 @@ def main():
                            "frac_of_sustained": round(flops / t / (pk["bf16_tflops_sustained"] * 1e12), 4),
                            "tflop": round(flops / 1e12, 3)}
         points = {}
+        # The headline's batch again with 40 warm-up steps: for the 14 steps after a 4,096-token prefill the SM
+        # clock is still 1.4 GHz under the power cap's after-effect (then 1.85 GHz), and a decode step follows it.
+        k = max(16, args.steps // 2)
+        s, ctx, _ = time_decode(infer, args.batch, k, 40, seed=2, checks=checks)
+        byts, _, _ = decode_bytes(cfg, args.layers, args.batch * ctx, esize)
+        points[f"decode_b{args.batch}_settled"] = round(args.batch * k / s, 2)
+        points[f"decode_b{args.batch}_settled_frac"] = round(byts / (s / k) / 1e9 / pk["hbm_gbs"], 4)
         for b in (1, 64, 128):        # 128 sequences: beyond the 64-token tiles of the decode products
             k = max(16, args.steps // 2)
             s, ctx, _ = time_decode(infer, b, k, args.warmup, seed=3 + b, checks=checks)
