@@ -445,7 +445,7 @@ def main():
         points[f"decode_b{args.batch}_settled_frac"] = round(byts / (s / k) / 1e9 / pk["hbm_gbs"], 4)
         for b in (1, 64, 128):        # 128 sequences: beyond the 64-token tiles of the decode products
             k = max(16, args.steps // 2)
-            s, ctx, _ = time_decode(infer, b, k, args.warmup, seed=3 + b, checks=checks)
+            s, ctx, _ = time_decode(infer, b, k, max(args.warmup, 40), seed=3 + b, checks=checks)     # settled, as above
             byts, _, _ = decode_bytes(cfg, args.layers, b * ctx, esize)
             points[f"decode_b{b}"] = round(b * k / s, 2)
             points[f"decode_b{b}_frac"] = round(byts / (s / k) / 1e9 / pk["hbm_gbs"], 4)
