@@ -483,12 +483,17 @@ def gemm_skinny_stream(w: torch.Tensor, a: torch.Tensor, row_scale=None, sink=No
 #   512 tokens: q/k/v (96) 27.6 / 34.1, output (64) 24.2 / 21.9, down (64) 70.2 / 58.5
 # and on the 1B shape at 128 tokens: gate/up (64 tiles) 18.0 / 25.9.  So beyond 64 tokens: weights as rows
 # while the other way has fewer tiles than 0.6 of the SMs; the gate/up product, whose K range cannot be
-# cut (its epilogue needs whole sums), while it has fewer than a third of them.
+# cut (its epilogue needs whole sums), while it has fewer than a third of them, and already from 33 tokens on
+# (8B shape, ms per decode step with the gate/up product's weights / tokens as rows: 48 sequences 4.06 / 4.02,
+# 64 sequences 4.44 / 4.36; 24 and 32 sequences, were they included: 3.42 / 3.49 and 3.52 / 3.62).
 SKINNY_MAX_ROWS = 512
 
 
+SWIGLU_WEIGHT_ROWS_MAX = 32     # tokens up to which the gate/up product takes the weights as tile rows
+
+
 def weights_as_rows(M: int, N: int, swiglu: bool = False) -> bool:
-    if M <= 64:
+    if M <= (SWIGLU_WEIGHT_ROWS_MAX if swiglu else 64):
         return True
     if M > SKINNY_MAX_ROWS:
         return False
