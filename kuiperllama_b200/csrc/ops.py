@@ -6,7 +6,6 @@ missing extension or a refused size raises.
 from __future__ import annotations
 
 import ctypes
-import os
 import threading
 from typing import Dict, Optional
 
