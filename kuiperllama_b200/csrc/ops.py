@@ -375,7 +375,8 @@ def skinny_splits(N: int, K: int, M: int = 1) -> int:
     of the weights' (pieces * M * 4 <= K * 2 / 4)."""
     tiles = ((N + 127) // 128) * max(1, (M + 127) // 128)    # CTAs per cut: weight tiles x token tiles (of 128 beyond 64 tokens)
     k_blocks = (K + 63) // 64
-    want = max(1, min((2 * sm_count() + tiles // 2) // tiles, k_blocks // 4, 32, max(1, K // (8 * max(M, 1)))))
+    # never more CTAs than the two per SM that are resident at once: one CTA too many is a second round
+    want = max(1, min((2 * sm_count()) // tiles, k_blocks // 4, 32, max(1, K // (8 * max(M, 1)))))
     per = (k_blocks + want - 1) // want
     return (k_blocks + per - 1) // per
 
