@@ -217,9 +217,10 @@ __device__ __forceinline__ void make_token_qkv(const DecodeFuse& fuse, bf16* q_s
 }
 
 // SK: keys per stage, a cache page (64) or half of one.  Half pages with two warps make a CTA of the
-// decode layout light enough (48 KB of stages at a head size of 128) for four of them on an SM.
+// decode layout light enough (48 KB of stages at a head size of 128) for four of them on an SM, or
+// with two stages (32 KB) for six.
 template <int HD, int WM, int WN, int NS, int SK>
-__global__ void __launch_bounds__(32 * WM * WN, SK < PAGE ? 4 : (NS == 2 ? ((HD == 64 && WN > 1) ? 4 : 3) : 2))   // whole pages, NS = 2: three CTAs per SM (168 registers, 3 x 64 KB of stages); four in the decode layout with a head size of 64
+__global__ void __launch_bounds__(32 * WM * WN, SK < PAGE ? (NS == 2 ? 6 : 4) : (NS == 2 ? ((HD == 64 && WN > 1) ? 4 : 3) : 2))   // half pages: six CTAs of two stages or four of three; whole pages, NS = 2: three CTAs per SM (168 registers, 3 x 64 KB of stages), four in the decode layout with a head size of 64
 attention_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out,
                      const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                      const int* __restrict__ block_table, int blocks_per_seq,
@@ -644,6 +645,11 @@ static int attention_mma_dispatch(const void* q, int q_stride, void* out, const 
         const long long rounds2 = (ctas + 3 * sms - 1) / (3 * sms), rounds3 = (ctas + 2 * sms - 1) / (2 * sms);
         // More CTAs than three per SM: light CTAs (two warps, half pages, three stages), four to an SM.
         static const int light = getenv("KL_ATTN_LIGHT") ? atoi(getenv("KL_ATTN_LIGHT")) : 1;
+        // Light CTAs of two stages (32 KB, 168 registers) fit six to an SM: taken where that saves rounds
+        // over four of three stages (each of its rounds moves fewer bytes at a time; measured on the 8B
+        // shape: one round against two and two against three are faster, three against four is not).
+        const long long rounds4 = (ctas + 4 * sms - 1) / (4 * sms), rounds6 = (ctas + 6 * sms - 1) / (6 * sms);
+        if (rounds2 > 1 && light && rounds6 * 7 < rounds4 * 5) KL_MMA5(128, 1, 2, 2, 32);
         if (rounds2 > 1 && light) KL_MMA5(128, 1, 2, 3, 32);
         if (rounds2 > 1 && rounds3 <= rounds2) KL_MMA(128, 1, 4, 3);
     }

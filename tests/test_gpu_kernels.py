@@ -503,7 +503,9 @@ def test_attention_mma_prefill(ops, H, KV, hd, window):
 # the cases with 7 * KV * splits > 444 take the light CTAs (two warps, half pages) of the head size 128
 @pytest.mark.parametrize("H,KV,hd,window,splits", [(8, 2, 128, 0, 1), (32, 8, 128, 0, 5), (4, 4, 64, 0, 3), (6, 2, 64, 0, 16),
                                                    (8, 8, 128, 100, 2), (16, 1, 128, 0, 4), (32, 8, 128, 0, 9), (8, 8, 128, 100, 8),
-                                                   (64, 64, 128, 0, 2), (24, 8, 128, 33, 16)])
+                                                   (64, 64, 128, 0, 2), (24, 8, 128, 33, 16),
+                                                   # 592 < 7 * KV * splits <= 888: light CTAs of two stages, six per SM
+                                                   (32, 8, 128, 0, 12), (8, 8, 128, 100, 11)])
 def test_attention_mma_decode(ops, H, KV, hd, window, splits):
     seqs = [(199, 1), (0, 1), (64, 1), (128, 1), (63, 1), (249, 1), (1000, 1)]
     cache, slots, ks, vs, qbuf, stride, cu, sl, st, nw, rows = _ragged_problem(H, KV, hd, seqs, seed=16)
@@ -517,10 +519,10 @@ def test_attention_mma_decode(ops, H, KV, hd, window, splits):
         _close(out[i].view(H, hd), ref, "bfloat16", f"mma decode seq {i} (len {s0 + 1})", scale=float(vs[i].abs().max()))
 
 
-@pytest.mark.parametrize("few_rows,splits,KV", [(False, 1, 2), (True, 1, 2), (True, 7, 2), (True, 29, 16)])
+@pytest.mark.parametrize("few_rows,splits,KV", [(False, 1, 2), (True, 1, 2), (True, 7, 2), (True, 29, 16), (True, 40, 16)])
 def test_attention_mma_finds_one_far_key_among_thousands(ops, few_rows, splits, KV):
-    """With 16 kv heads and 29 pieces the decode layout's light CTAs run (half pages): the far keys
-    also sit at the ends of half pages."""
+    """With 16 kv heads and 29 or 40 pieces the decode layout's light CTAs run (half pages; four or six
+    per SM): the far keys also sit at the ends of half pages."""
     torch.manual_seed(17)
     dt = torch.bfloat16
     H, hd, n = max(8, KV), 128, 3000
@@ -629,7 +631,8 @@ def test_gate_up_product_with_swiglu_epilogue(ops, M, I, K):
 @pytest.mark.parametrize("H,KV,hd,window,splits,pieces", [(8, 2, 128, 0, 1, 0), (32, 8, 128, 0, 5, 6), (4, 4, 64, 0, 3, 2),
                                                           (6, 2, 64, 0, 16, 0), (8, 8, 128, 100, 2, 3), (16, 1, 128, 0, 4, 1),
                                                           (32, 8, 128, 0, 9, 6), (8, 8, 128, 100, 8, 0), (64, 64, 128, 0, 2, 1),
-                                                          (24, 8, 128, 33, 16, 9), (64, 8, 128, 0, 9, 3)])
+                                                          (24, 8, 128, 33, 16, 9), (64, 8, 128, 0, 9, 3),
+                                                          (32, 8, 128, 0, 12, 6), (8, 8, 128, 100, 11, 0), (48, 16, 128, 0, 7, 2)])
 def test_attention_decode_fused(ops, H, KV, hd, window, splits, pieces):
     """Rotation of q and k, the cache write, attention and the split merge in one kernel, against
     the separate rotary kernel followed by the reference attention; twice, so that the counters

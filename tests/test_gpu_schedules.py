@@ -120,7 +120,7 @@ def test_a_fresh_prompt_joins_decoding_sequences(models, name, dtype):
     engine.check_device_errors()
 
 
-@pytest.mark.parametrize("batch", [8, 20, 33, 64, 96, 130])
+@pytest.mark.parametrize("batch", [8, 20, 33, 64, 80, 96, 130])
 @pytest.mark.parametrize("name", CONFIGS)
 def test_graph_decode_at_larger_batches(models, name, batch):
     """bfloat16 decode steps replayed from a CUDA graph at batch sizes that take the 16-, 32-, 64- and
